@@ -1,0 +1,199 @@
+/*
+ * scorch_b200 — C ABI of the B200 (sm_100a) sparse kernels that replace the CPU/OpenMP kernels
+ * behind scorch.matmul / scorch.einsum.
+ *
+ * Conventions
+ *   - Every pointer argument is a DEVICE pointer unless its name ends in "_host".
+ *   - Index arrays are int32, values are 1-D, dense operands are row-major with an explicit
+ *     leading dimension (elements), exactly the arrays the reference hands to its kernels
+ *     (reference: src/scorch/prebuilt_kernels.py:211-218, src/scorch/storage.py:46-51).
+ *   - Sizes are 64-bit.  Where the reference keeps a size in a 32-bit int (csrc/spmm.h:113,
+ *     csrc/kernels.h:110,520) and the value would not fit, the call returns SB_ERR_OVERFLOW
+ *     instead of wrapping.
+ *   - `stream` is a cudaStream_t passed as void*.  Calls are asynchronous on that stream unless
+ *     stated otherwise.  Nothing here allocates device memory: outputs and workspaces are the
+ *     caller's, sized with the *_bytes() queries.
+ *   - Return value: 0 (SB_OK) or an SB_ERR_* code; sb_last_error() gives the message of the
+ *     last failing call on the calling thread.  No call throws, none falls back to the CPU.
+ *
+ * Reference-side binding: each entry point names the reference function it replaces
+ * (path:line inside the reference project).
+ */
+#ifndef SCORCH_B200_H_
+#define SCORCH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SB_API __attribute__((visibility("default")))
+#else
+#define SB_API
+#endif
+
+enum {
+  SB_OK = 0,
+  SB_ERR_INVALID_ARG = 1, /* null pointer, negative size, misaligned or inconsistent shapes */
+  SB_ERR_CUDA = 2,        /* a CUDA runtime call or launch failed; see sb_last_error() */
+  SB_ERR_OVERFLOW = 3,    /* a quantity the reference stores as int32 does not fit */
+  SB_ERR_WORKSPACE = 4,   /* workspace/scratch smaller than the matching *_bytes() query */
+  SB_ERR_UNSUPPORTED = 5  /* dtype or shape outside what the kernels implement */
+};
+
+/* value dtypes of the typed entry points; suffixes follow csrc/prebuilt_types.h:36-62 */
+enum { SB_F32 = 0, SB_F64 = 1, SB_I32 = 2, SB_I64 = 3 };
+
+SB_API int sb_abi_version(void);
+SB_API const char* sb_status_string(int status);
+SB_API const char* sb_last_error(void);
+
+/* --------------------------------------------------------------------------------------------
+ * Row plan: the nnz-balanced split of a CSR matrix that SpMM and SpMV use.  Rows with more than
+ * SB_HEAVY_ROW_NNZ stored entries ("heavy" rows, e.g. hubs of a power-law graph) are cut into
+ * segments of SB_HEAVY_ROW_NNZ entries; one CTA sums one segment in shared memory and a
+ * fixed-order second stage adds the segment sums, so results do not depend on scheduling.
+ * The plan depends only on `pos`; build it once per matrix and reuse it.
+ * Replaces: the atomic work-stealing row loop of csrc/spmm.h:2032-2046 and the
+ * schedule(dynamic,16) / schedule(static) loops of csrc/spmm.h:121, csrc/kernels.h:32.
+ * -------------------------------------------------------------------------------------------- */
+#define SB_HEAVY_ROW_NNZ 1024
+
+/* bytes of device memory a plan for (m rows, nnz entries) needs (worst case over all patterns) */
+SB_API size_t sb_csr_plan_bytes(int64_t m, int64_t nnz);
+/* upper bound on the number of heavy-row segments of any matrix with nnz entries */
+SB_API int64_t sb_csr_plan_max_segments(int64_t nnz);
+/* asynchronous; `plan` must hold sb_csr_plan_bytes(m, nnz) bytes and be 16-byte aligned */
+SB_API int sb_csr_plan_build(int64_t m, int64_t nnz, const int32_t* pos, void* plan,
+                             size_t plan_bytes, void* stream);
+/* synchronises `stream`; returns the exact counts so callers can size scratch tightly */
+SB_API int sb_csr_plan_counts(const void* plan, int64_t* heavy_rows_host, int64_t* segments_host,
+                              void* stream);
+
+/* nnz-balanced contiguous row blocks for sharding one matrix over `parts` GPUs:
+ * bounds[g] = first row of block g (bounds[parts] = m); block g starts at the first row whose
+ * pos[] reaches g*nnz/parts.  `bounds` is a DEVICE array of parts+1 int64.  No reference
+ * counterpart: the reference is single-process. */
+SB_API int sb_partition_rows_by_nnz(int64_t m, const int32_t* pos, int parts, int64_t* bounds,
+                                    void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * CSR x dense SpMM, fp32, with optional fused bias and ReLU:
+ *     C[i, 0:k] = act( bias[0:k] + sum_p val[p] * B[crd[p], 0:k] ),  p in [pos[i], pos[i+1])
+ * Rows without entries give act(bias) (zeros when bias is NULL).
+ * Replaces: spmm_csr_float_v2 csrc/spmm.h:2007-2089, spmm_csr_typed<float> csrc/spmm.h:91-150,
+ *           spmm_csr_bias_act<float,relu> csrc/spmm.h:28-89 (bias != NULL; relu = 0/1), and the
+ *           compiler-emitted SpMM loop (src/scorch/compiler/cin_lowerer.py:3616-3667).
+ * `plan` may be NULL (every row is then handled by one warp).  `plan_segments` is the number of
+ * heavy segments to launch for: the exact count from sb_csr_plan_counts(), or -1 for the
+ * worst-case bound.  `scratch` must hold sb_spmm_csr_scratch_bytes(plan_segments or bound, k).
+ * ldb/ldc are in elements; B, C, bias must be 16-byte aligned and ldb, ldc multiples of 4 for
+ * the vector path (other layouts take a scalar path).  `batch` independent products with the
+ * same sparsity structure: val/B/C advance by their strides (elements) per batch item;
+ * stride_val may be 0 to share the values.
+ * -------------------------------------------------------------------------------------------- */
+SB_API size_t sb_spmm_csr_scratch_bytes(int64_t segments, int64_t k, int64_t batch);
+SB_API int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                           const int32_t* crd, const float* val, const float* B, int64_t ldb,
+                           const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
+                           int64_t stride_val, int64_t stride_b, int64_t stride_c,
+                           const void* plan, int64_t plan_segments, void* scratch,
+                           size_t scratch_bytes, void* stream);
+
+/* Same product for the other registry dtypes (SB_F64, SB_I32, SB_I64; SB_F32 also accepted).
+ * Integer products wrap like the reference's C++ arithmetic.
+ * Replaces: prebuilt_spmm_csr_{f64,i32,i64}, spmm_csr_double (csrc/ops.cpp:91-116). */
+SB_API int sb_spmm_csr_typed(int dtype, int64_t m, int64_t n, int64_t k, int64_t nnz,
+                             const int32_t* pos, const int32_t* crd, const void* val,
+                             const void* B, int64_t ldb, void* C, int64_t ldc, void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * CSR SpMV: y[i] = sum_p val[p] * x[crd[p]].  Every y[i] is written.
+ * Replaces: spmv_csr<T> csrc/kernels.h:12-49 (prebuilt_spmv_csr_{f32,f64,i32,i64}) and the
+ *           compiler-emitted loop of scorch.ops.spmv (src/scorch/ops.py:48-136).
+ * The fp32 entry uses the row plan (may be NULL) and a scratch of sb_spmv_csr_scratch_bytes().
+ * -------------------------------------------------------------------------------------------- */
+SB_API size_t sb_spmv_csr_scratch_bytes(int64_t segments);
+SB_API int sb_spmv_csr_f32(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                           const int32_t* crd, const float* val, const float* x, float* y,
+                           const void* plan, int64_t plan_segments, void* scratch,
+                           size_t scratch_bytes, void* stream);
+SB_API int sb_spmv_csr_typed(int dtype, int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                             const int32_t* crd, const void* val, const void* x, void* y,
+                             void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * SDDMM: out_val[p] = mask_val[p] * dot(Q[i_p, 0:d], K[j_p, 0:d]) for every stored (i_p, j_p) of
+ * the mask, in the mask's entry order.  mask_val may be NULL (all ones).  K is (n, d) row-major,
+ * i.e. the "ij,ik,jk->ij" operand; for "ij,ik,kj->ij" the reference transposes K first
+ * (src/scorch/ops.py:534-540) and so does the host shim.
+ * CSR mask  — replaces the compiler-emitted scalar-accumulator loop (generator:
+ *             src/scorch/ops.py:638-664, src/scorch/compiler/iter_lattice.py:1011-1098,
+ *             src/scorch/compiler/cin_lowerer.py:2286-2326); like it, writes fresh int32
+ *             coordinate arrays out_row/out_col when they are non-NULL.
+ * COO mask  — replaces sddmm_coo_float_prebuilt csrc/kernels.h:508-570 (output shares the
+ *             input's coordinate arrays, so none are written).
+ * `batch` independent (Q, K) pairs share the mask: Q/K/out_val advance by their strides
+ * (elements); mask_val is shared.
+ * -------------------------------------------------------------------------------------------- */
+SB_API int sb_sddmm_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t* pos,
+                            const int32_t* crd, const float* mask_val, const float* Q,
+                            int64_t ldq, const float* K, int64_t ldk, float* out_val,
+                            int32_t* out_row, int32_t* out_col, int64_t batch, int64_t stride_q,
+                            int64_t stride_k, int64_t stride_out, void* stream);
+SB_API int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t* row,
+                            const int32_t* col, const float* mask_val, const float* Q,
+                            int64_t ldq, const float* K, int64_t ldk, float* out_val,
+                            int64_t batch, int64_t stride_q, int64_t stride_k,
+                            int64_t stride_out, void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Row softmax over the stored entries of a CSR matrix: out[p] = exp(scale*v[p] - max_row) / sum.
+ * Rows without entries are untouched.  in == out is allowed.
+ * Replaces: the caller-side torch scatter code between SDDMM and SpMM,
+ *           bench/bench_sparse_transformer.py:277-297 (scale = 1) and its `values * scale`
+ *           pre-multiplication (bench/bench_sparse_transformer.py:363-366).
+ * -------------------------------------------------------------------------------------------- */
+SB_API int sb_csr_row_softmax_f32(int64_t m, int64_t nnz, const int32_t* pos, const float* in,
+                                  float* out, float scale, int64_t batch, int64_t stride,
+                                  void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * CSR x CSR SpGEMM (Gustavson), two phases.  Output rows have strictly ascending, unique
+ * columns; the structure is the symbolic union (entries whose products cancel are kept).
+ * Replaces: spmspm_csr<T> csrc/kernels.h:51-202 (prebuilt_spmspm_csr_{f32,f64,i32,i64},
+ *           spmspm_csr_float) and the compiler-emitted two-phase code
+ *           (src/scorch/compiler/cin_lowerer.py:2683+).
+ *   symbolic: fills Cpos[0..m] (int32) and returns the total in *total_nnz_host; SYNCHRONISES the
+ *             stream (the caller must size Ccrd/Cval).  SB_ERR_OVERFLOW when total >= 2^31.
+ *   numeric : fills Ccrd/Cval for the Cpos of the symbolic call; `ws` must be the SAME,
+ *             unmodified workspace (it carries the row bins).
+ * A has m rows; B has `kb` rows and n columns.
+ * -------------------------------------------------------------------------------------------- */
+SB_API size_t sb_spgemm_workspace_bytes(int64_t m, int64_t n, int dtype);
+SB_API int sb_spgemm_symbolic(int64_t m, int64_t kb, int64_t n, const int32_t* Apos,
+                              const int32_t* Acrd, const int32_t* Bpos, const int32_t* Bcrd,
+                              int32_t* Cpos, int64_t* total_nnz_host, void* ws, size_t ws_bytes,
+                              void* stream);
+SB_API int sb_spgemm_numeric(int dtype, int64_t m, int64_t kb, int64_t n, const int32_t* Apos,
+                             const int32_t* Acrd, const void* Aval, const int32_t* Bpos,
+                             const int32_t* Bcrd, const void* Bval, const int32_t* Cpos,
+                             int32_t* Ccrd, void* Cval, void* ws, size_t ws_bytes, void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Format plumbing on the device (the reference does these with torch ops before dispatch,
+ * src/scorch/stensor.py:785-896): sorted COO rows -> CSR row pointers, CSR row pointers -> row
+ * ids.
+ * -------------------------------------------------------------------------------------------- */
+SB_API int sb_coo_rows_to_csr_pos(int64_t m, int64_t nnz, const int32_t* row_sorted,
+                                  int32_t* pos, void* stream);
+SB_API int sb_csr_pos_to_coo_rows(int64_t m, int64_t nnz, const int32_t* pos, int32_t* row,
+                                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCORCH_B200_H_ */

@@ -1,0 +1,204 @@
+"""numpy front end of the CPU oracle (``liboracle.so`` built from ``scorch_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY — imported by ``tests/``, the smoke check and the CPU-baseline legs of
+the benchmark; never by the product package.  Each function names the reference kernel it
+checks against (paths relative to the reference project).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lib = None
+
+_I32 = np.int32
+_SUFFIX = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
+           np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}
+
+
+def build(force: bool = False) -> str:
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "scorch_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE] + (["-B"] if force else []))
+    return so
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.so_spgemm_symbolic.restype = C.c_int64
+        _lib.so_num_threads.restype = C.c_int
+    return _lib
+
+
+def num_threads() -> int:
+    return int(lib().so_num_threads())
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def spmm_csr_v2(pos, crd, val, B, tile: int = 256):
+    """spmm_csr_float_v2, csrc/spmm.h:2007-2089."""
+    pos, crd, val, B = _c(pos, _I32), _c(crd, _I32), _c(val, np.float32), _c(B, np.float32)
+    m, k = len(pos) - 1, B.shape[1]
+    out = np.empty((m, k), np.float32)
+    lib().so_spmm_csr_f32_v2(C.c_int(m), C.c_int(k), _p(pos), _p(crd), _p(val), _p(B), _p(out),
+                             C.c_int(tile))
+    return out
+
+
+def spmm_csr_typed(pos, crd, val, B):
+    """spmm_csr_typed<T>, csrc/spmm.h:91-150."""
+    val = np.ascontiguousarray(val)
+    sfx = _SUFFIX[val.dtype]
+    pos, crd, B = _c(pos, _I32), _c(crd, _I32), _c(B, val.dtype)
+    m, k = len(pos) - 1, B.shape[1]
+    out = np.empty((m, k), val.dtype)
+    getattr(lib(), "so_spmm_csr_" + sfx)(C.c_int(m), C.c_int(k), _p(pos), _p(crd), _p(val),
+                                          _p(B), _p(out))
+    return out
+
+
+def spmm_csr_bias_act(pos, crd, val, B, bias, relu: bool):
+    """spmm_csr_bias_act<float, relu>, csrc/spmm.h:28-89."""
+    pos, crd, val, B = _c(pos, _I32), _c(crd, _I32), _c(val, np.float32), _c(B, np.float32)
+    bias = _c(bias, np.float32)
+    m, k = len(pos) - 1, B.shape[1]
+    out = np.empty((m, k), np.float32)
+    lib().so_spmm_csr_bias_act_f32(C.c_int(m), C.c_int(k), _p(pos), _p(crd), _p(val), _p(B),
+                                   _p(bias), C.c_int(int(relu)), _p(out))
+    return out
+
+
+def spmv_csr(pos, crd, val, x):
+    """spmv_csr<T>, csrc/kernels.h:12-49."""
+    val = np.ascontiguousarray(val)
+    sfx = _SUFFIX[val.dtype]
+    pos, crd, x = _c(pos, _I32), _c(crd, _I32), _c(x, val.dtype)
+    m = len(pos) - 1
+    y = np.empty(m, val.dtype)
+    getattr(lib(), "so_spmv_csr_" + sfx)(C.c_int(m), _p(pos), _p(crd), _p(val), _p(x), _p(y))
+    return y
+
+
+def sddmm_coo(row, col, sval, A, B):
+    """sddmm_coo_float_prebuilt, csrc/kernels.h:508-570."""
+    row, col, sval = _c(row, _I32), _c(col, _I32), _c(sval, np.float32)
+    A, B = _c(A, np.float32), _c(B, np.float32)
+    out = np.empty(len(sval), np.float32)
+    lib().so_sddmm_coo_f32(C.c_int64(len(sval)), C.c_int(A.shape[1]), _p(row), _p(col), _p(sval),
+                           _p(A), _p(B), _p(out))
+    return out
+
+
+def sddmm_csr(pos, crd, mval, Q, K):
+    """Compiler-emitted SDDMM for a CSR mask (generator: src/scorch/ops.py:638-664).
+    Returns (row, col, val) like the reference's all-COO output."""
+    pos, crd, mval = _c(pos, _I32), _c(crd, _I32), _c(mval, np.float32)
+    Q, K = _c(Q, np.float32), _c(K, np.float32)
+    nnz = len(crd)
+    r, c, v = np.empty(nnz, _I32), np.empty(nnz, _I32), np.empty(nnz, np.float32)
+    lib().so_sddmm_csr_f32(C.c_int(len(pos) - 1), C.c_int(Q.shape[1]), _p(pos), _p(crd),
+                           _p(mval), _p(Q), _p(K), _p(r), _p(c), _p(v))
+    return r, c, v
+
+
+def csr_row_softmax(pos, val):
+    """_sparse_softmax_csr_vectorized, bench/bench_sparse_transformer.py:277-297."""
+    pos, val = _c(pos, _I32), _c(val, np.float32)
+    out = val.copy()
+    lib().so_csr_row_softmax_f32(C.c_int(len(pos) - 1), _p(pos), _p(val), _p(out))
+    return out
+
+
+def spgemm_symbolic(Apos, Acrd, Bpos, Bcrd, n: int):
+    """Symbolic phase of spmspm_csr<T>, csrc/kernels.h:69-111.  Returns (Cpos int32, total)."""
+    Apos, Acrd, Bpos, Bcrd = (_c(a, _I32) for a in (Apos, Acrd, Bpos, Bcrd))
+    m = len(Apos) - 1
+    cpos = np.empty(m + 1, _I32)
+    total = lib().so_spgemm_symbolic(C.c_int(m), C.c_int(n), _p(Apos), _p(Acrd), _p(Bpos),
+                                     _p(Bcrd), _p(cpos))
+    return cpos, int(total)
+
+
+def spgemm(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n: int):
+    """spmspm_csr<T>, csrc/kernels.h:51-202.  Returns (Cpos, Ccrd, Cval)."""
+    Aval = np.ascontiguousarray(Aval)
+    sfx = _SUFFIX[Aval.dtype]
+    Apos, Acrd, Bpos, Bcrd = (_c(a, _I32) for a in (Apos, Acrd, Bpos, Bcrd))
+    Bval = _c(Bval, Aval.dtype)
+    m = len(Apos) - 1
+    cpos, total = spgemm_symbolic(Apos, Acrd, Bpos, Bcrd, n)
+    if total >= 2 ** 31:
+        raise OverflowError("SpGEMM output does not fit int32 row pointers")
+    ccrd, cval = np.empty(total, _I32), np.empty(total, Aval.dtype)
+    getattr(lib(), "so_spgemm_numeric_" + sfx)(C.c_int(m), C.c_int(n), _p(Apos), _p(Acrd),
+                                                _p(Aval), _p(Bpos), _p(Bcrd), _p(Bval),
+                                                _p(cpos), _p(ccrd), _p(cval))
+    return cpos, ccrd, cval
+
+
+# ---- float64 tolerance oracles ------------------------------------------------------------
+def spmm_csr_acc64(pos, crd, val, B, bias=None, relu: bool = False):
+    pos, crd, val, B = _c(pos, _I32), _c(crd, _I32), _c(val, np.float32), _c(B, np.float32)
+    bias = None if bias is None else _c(bias, np.float32)
+    m, k = len(pos) - 1, B.shape[1]
+    out = np.empty((m, k), np.float64)
+    lib().so_spmm_csr_acc64(C.c_int(m), C.c_int(k), _p(pos), _p(crd), _p(val), _p(B), _p(bias),
+                            C.c_int(int(relu)), _p(out))
+    return out
+
+
+def spmv_csr_acc64(pos, crd, val, x):
+    pos, crd, val, x = _c(pos, _I32), _c(crd, _I32), _c(val, np.float32), _c(x, np.float32)
+    y = np.empty(len(pos) - 1, np.float64)
+    lib().so_spmv_csr_acc64(C.c_int(len(pos) - 1), _p(pos), _p(crd), _p(val), _p(x), _p(y))
+    return y
+
+
+def sddmm_csr_acc64(pos, crd, mval, Q, K):
+    pos, crd = _c(pos, _I32), _c(crd, _I32)
+    mval = None if mval is None else _c(mval, np.float32)
+    Q, K = _c(Q, np.float32), _c(K, np.float32)
+    out = np.empty(len(crd), np.float64)
+    lib().so_sddmm_csr_acc64(C.c_int(len(pos) - 1), C.c_int(Q.shape[1]), _p(pos), _p(crd),
+                             _p(mval), _p(Q), _p(K), _p(out))
+    return out
+
+
+def csr_row_softmax_acc64(pos, val):
+    pos, val = _c(pos, _I32), _c(val, np.float64)
+    out = val.copy()
+    lib().so_csr_row_softmax_acc64(C.c_int(len(pos) - 1), _p(pos), _p(val), _p(out))
+    return out
+
+
+def spgemm_values_acc64(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n, Cpos, Ccrd):
+    Apos, Acrd, Bpos, Bcrd, Cpos, Ccrd = (_c(a, _I32) for a in (Apos, Acrd, Bpos, Bcrd, Cpos, Ccrd))
+    Aval, Bval = _c(Aval, np.float32), _c(Bval, np.float32)
+    out = np.empty(len(Ccrd), np.float64)
+    lib().so_spgemm_numeric_acc64(C.c_int(len(Apos) - 1), C.c_int(n), _p(Apos), _p(Acrd), _p(Aval),
+                                  _p(Bpos), _p(Bcrd), _p(Bval), _p(Cpos), _p(Ccrd), _p(out))
+    return out
+
+
+def allclose_report(got, want64, rtol=1e-4, atol=1e-5):
+    """(ok, max_abs_err, n_violations) of |got - want| <= atol + rtol*|want| in float64."""
+    got = np.asarray(got, dtype=np.float64).ravel()
+    want64 = np.asarray(want64, dtype=np.float64).ravel()
+    err = np.abs(got - want64)
+    bad = err > (atol + rtol * np.abs(want64))
+    ok = (not bad.any()) and bool(np.isfinite(got).all())
+    return ok, (float(err.max()) if err.size else 0.0), int(bad.sum())

@@ -1,0 +1,276 @@
+// SDDMM (sampled dense-dense product) over the stored entries of a CSR or COO mask, and the row
+// softmax over CSR values that sits between SDDMM and SpMM in sparse attention.
+//
+// SDDMM work split: the entry list is cut into chunks of 32 consecutive entries, one warp per
+// chunk, so the split is balanced by nnz whatever the row lengths are.  The warp reads the
+// chunk's column ids / mask values with one coalesced load, finds each entry's row (one binary
+// search per warp plus a short per-lane refinement when a chunk crosses rows), then G lanes
+// compute one dot product with 128-bit loads of the K row and a shuffle tree; the Q row stays in
+// registers while consecutive entries share it.  Results are written back one coalesced line
+// per chunk.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int kSddmmWarps = 8;
+
+struct SddmmArgs {
+  int m;
+  int d;
+  long long nnz;
+  const int* pos;   // CSR mask (null for COO)
+  const int* row;   // COO mask (null for CSR)
+  const int* crd;
+  const float* mask_val;  // may be null
+  const float* Q;
+  long long ldq;
+  const float* K;
+  long long ldk;
+  float* out_val;
+  int* out_row;  // optional fresh coordinates (CSR variant)
+  int* out_col;
+  long long stride_q, stride_k, stride_out;
+};
+
+// Row ids of the 32 entries [p0, p0+32) of a CSR matrix, one per lane.
+__device__ __forceinline__ int chunk_rows(const int* __restrict__ pos, int m, long long p0,
+                                          int cnt, int lane) {
+  // warp-uniform: row of the first entry
+  const int r0 = row_of_entry(pos, 0, m, (int)p0);
+  int r = r0;
+  const int last = (int)p0 + cnt - 1;
+  if (__ldg(pos + r0 + 1) <= last) {  // chunk crosses a row boundary
+    const int p = (int)p0 + min(lane, cnt - 1);
+    r = row_of_entry(pos, r0, m, p);
+  }
+  return r;
+}
+
+template <int G, int VEC>
+__global__ void __launch_bounds__(kSddmmWarps * 32)
+sddmm_kernel(SddmmArgs a) {
+  constexpr int NG = 32 / G;  // entries in flight per step
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long chunk = (long long)blockIdx.x * kSddmmWarps + warp;
+  const long long p0 = chunk * 32;
+  if (p0 >= a.nnz) return;
+  const int cnt = (int)min((long long)32, a.nnz - p0);
+  const long long bz = blockIdx.y;
+  const float* Q = a.Q + bz * a.stride_q;
+  const float* K = a.K + bz * a.stride_k;
+
+  int my_j = 0, my_i = 0;
+  float my_s = 1.f;
+  if (lane < cnt) {
+    my_j = ld_stream(a.crd + p0 + lane);
+    if (a.mask_val) my_s = ld_stream(a.mask_val + p0 + lane);
+    if (a.row) my_i = ld_stream(a.row + p0 + lane);
+  }
+  if (a.pos) my_i = chunk_rows(a.pos, a.m, p0, cnt, lane);
+  if (bz == 0 && lane < cnt) {
+    if (a.out_row) a.out_row[p0 + lane] = my_i;
+    if (a.out_col) a.out_col[p0 + lane] = my_j;
+  }
+
+  const int g = lane / G, l = lane % G;
+  bool col_ok[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; v++) col_ok[v] = (l + v * G) * 4 < a.d;
+
+  float4 q[VEC];
+  int q_row = -1;
+  float my_res = 0.f;
+  constexpr int U = (G >= 4) ? 4 : G;  // steps unrolled together: U K-row loads in flight
+#pragma unroll 1
+  for (int s0 = 0; s0 < G; s0 += U) {
+    int jj[U], ii[U];
+    float4 kv[U][VEC];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int idx = (s0 + u) * NG + g;
+      jj[u] = __shfl_sync(FULL, my_j, idx);
+      ii[u] = __shfl_sync(FULL, my_i, idx);
+      ok[u] = idx < cnt;
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const float* krow = K + (long long)jj[u] * a.ldk;
+#pragma unroll
+      for (int v = 0; v < VEC; v++)
+        kv[u][v] = (ok[u] && col_ok[v]) ? ldg4(krow + (l + v * G) * 4)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      if (ok[u] && ii[u] != q_row) {
+        q_row = ii[u];
+        const float* qrow = Q + (long long)q_row * a.ldq;
+#pragma unroll
+        for (int v = 0; v < VEC; v++)
+          q[v] = col_ok[v] ? ldg4(qrow + (l + v * G) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float part = 0.f;
+      if (ok[u]) {
+#pragma unroll
+        for (int v = 0; v < VEC; v++) part = dot4(q[v], kv[u][v], part);
+      }
+      part = group_sum<G>(part);
+      if (l == s0 + u) my_res = part;  // lane (g, l) keeps entry l*NG + g
+    }
+  }
+  const int my_idx = l * NG + g;
+  const float s = __shfl_sync(FULL, my_s, my_idx);
+  if (my_idx < cnt) a.out_val[bz * a.stride_out + p0 + my_idx] = s * my_res;
+}
+
+// Any d / any alignment: one lane per entry, scalar loop over d.
+__global__ void sddmm_generic_kernel(SddmmArgs a) {
+  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= a.nnz) return;
+  const long long bz = blockIdx.y;
+  const int j = a.crd[p];
+  const int i = a.row ? a.row[p] : row_of_entry(a.pos, 0, a.m, (int)p);
+  const float* q = a.Q + bz * a.stride_q + (long long)i * a.ldq;
+  const float* k = a.K + bz * a.stride_k + (long long)j * a.ldk;
+  float acc = 0.f;
+  for (int c = 0; c < a.d; c++) acc = fmaf(q[c], k[c], acc);
+  a.out_val[bz * a.stride_out + p] = (a.mask_val ? a.mask_val[p] : 1.f) * acc;
+  if (bz == 0) {
+    if (a.out_row) a.out_row[p] = i;
+    if (a.out_col) a.out_col[p] = j;
+  }
+}
+
+template <int G, int VEC>
+static int launch_sddmm(const SddmmArgs& a, int64_t batch, cudaStream_t st) {
+  const long long chunks = ceil_div(a.nnz, 32);
+  dim3 grid((unsigned)ceil_div(chunks, kSddmmWarps), (unsigned)batch);
+  sddmm_kernel<G, VEC><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  SB_LAUNCH_CHECK("sddmm_kernel");
+  return SB_OK;
+}
+
+static int sddmm_dispatch(SddmmArgs a, int64_t batch, cudaStream_t st) {
+  if (a.nnz == 0) return SB_OK;
+  const bool vec_ok = (a.d % 4 == 0) && (a.ldq % 4 == 0) && (a.ldk % 4 == 0) && aligned16(a.Q) &&
+                      aligned16(a.K) && (a.stride_q % 4 == 0) && (a.stride_k % 4 == 0) &&
+                      a.d <= 512;
+  if (!vec_ok) {
+    dim3 grid((unsigned)ceil_div(a.nnz, 256), (unsigned)batch);
+    sddmm_generic_kernel<<<grid, 256, 0, st>>>(a);
+    SB_LAUNCH_CHECK("sddmm_generic_kernel");
+    return SB_OK;
+  }
+  if (a.d <= 16) return launch_sddmm<4, 1>(a, batch, st);
+  if (a.d <= 32) return launch_sddmm<8, 1>(a, batch, st);
+  if (a.d <= 64) return launch_sddmm<8, 2>(a, batch, st);
+  if (a.d <= 128) return launch_sddmm<16, 2>(a, batch, st);
+  if (a.d <= 256) return launch_sddmm<32, 2>(a, batch, st);
+  return launch_sddmm<32, 4>(a, batch, st);
+}
+
+// ---- CSR row softmax ------------------------------------------------------------------------
+constexpr int kSoftmaxRegs = 12;  // rows up to 32*12 = 384 entries stay in registers
+
+__global__ void __launch_bounds__(256)
+csr_row_softmax_kernel(int m, const int* __restrict__ pos, const float* __restrict__ in,
+                       float* __restrict__ out, float scale, long long stride) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= m) return;
+  const int b = __ldg(pos + row), e = __ldg(pos + row + 1);
+  if (b == e) return;
+  in += (long long)blockIdx.y * stride;
+  out += (long long)blockIdx.y * stride;
+  float v[kSoftmaxRegs];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int r = 0; r < kSoftmaxRegs; r++) {
+    const int p = b + lane + 32 * r;
+    v[r] = (p < e) ? in[p] * scale : -INFINITY;
+    mx = fmaxf(mx, v[r]);
+  }
+  for (int p = b + lane + 32 * kSoftmaxRegs; p < e; p += 32) mx = fmaxf(mx, in[p] * scale);
+  mx = group_max<32>(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int r = 0; r < kSoftmaxRegs; r++) {
+    const int p = b + lane + 32 * r;
+    v[r] = (p < e) ? expf(v[r] - mx) : 0.f;
+    sum += v[r];
+  }
+  for (int p = b + lane + 32 * kSoftmaxRegs; p < e; p += 32) sum += expf(in[p] * scale - mx);
+  sum = group_sum<32>(sum);
+  // tail first: it still needs the untouched input when in == out
+  for (int p = b + lane + 32 * kSoftmaxRegs; p < e; p += 32)
+    out[p] = expf(in[p] * scale - mx) / sum;
+#pragma unroll
+  for (int r = 0; r < kSoftmaxRegs; r++) {
+    const int p = b + lane + 32 * r;
+    if (p < e) out[p] = v[r] / sum;
+  }
+}
+
+static int check_sddmm(int64_t m, int64_t n, int64_t d, int64_t nnz, const void* crd,
+                       const void* Q, int64_t ldq, const void* K, int64_t ldk, const void* out,
+                       int64_t batch) {
+  SB_CHECK_ARG(m >= 0 && n >= 0 && d >= 0 && nnz >= 0, "sddmm: negative size");
+  SB_CHECK_ARG(m < INT32_MAX && n < INT32_MAX && d < INT32_MAX, "sddmm: dimension exceeds int32");
+  if (nnz > INT32_MAX)
+    return fail(SB_ERR_OVERFLOW, "sddmm: nnz=%lld does not fit int32", (long long)nnz);
+  SB_CHECK_ARG(nnz == 0 || (crd && out), "sddmm: null crd/out");
+  SB_CHECK_ARG(nnz == 0 || d == 0 || (Q && K), "sddmm: null Q/K");
+  SB_CHECK_ARG(ldq >= d && ldk >= d, "sddmm: leading dimension smaller than d");
+  SB_CHECK_ARG(batch >= 1 && batch <= 65535, "sddmm: batch must be in [1, 65535]");
+  return SB_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int sb_sddmm_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t* pos,
+                     const int32_t* crd, const float* mask_val, const float* Q, int64_t ldq,
+                     const float* K, int64_t ldk, float* out_val, int32_t* out_row,
+                     int32_t* out_col, int64_t batch, int64_t stride_q, int64_t stride_k,
+                     int64_t stride_out, void* stream) {
+  int rc = check_sddmm(m, n, d, nnz, crd, Q, ldq, K, ldk, out_val, batch);
+  if (rc != SB_OK) return rc;
+  SB_CHECK_ARG(pos, "sddmm_csr: pos is null");
+  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, mask_val, Q, ldq, K, ldk, out_val,
+              out_row, out_col, stride_q, stride_k, stride_out};
+  return sddmm_dispatch(a, batch, (cudaStream_t)stream);
+}
+
+int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t* row,
+                     const int32_t* col, const float* mask_val, const float* Q, int64_t ldq,
+                     const float* K, int64_t ldk, float* out_val, int64_t batch, int64_t stride_q,
+                     int64_t stride_k, int64_t stride_out, void* stream) {
+  int rc = check_sddmm(m, n, d, nnz, col, Q, ldq, K, ldk, out_val, batch);
+  if (rc != SB_OK) return rc;
+  SB_CHECK_ARG(nnz == 0 || row, "sddmm_coo: row is null");
+  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, mask_val, Q, ldq, K, ldk, out_val,
+              nullptr, nullptr, stride_q, stride_k, stride_out};
+  return sddmm_dispatch(a, batch, (cudaStream_t)stream);
+}
+
+int sb_csr_row_softmax_f32(int64_t m, int64_t nnz, const int32_t* pos, const float* in, float* out,
+                           float scale, int64_t batch, int64_t stride, void* stream) {
+  SB_CHECK_ARG(m >= 0 && m < INT32_MAX && nnz >= 0, "softmax: bad size");
+  if (nnz > INT32_MAX) return fail(SB_ERR_OVERFLOW, "softmax: nnz does not fit int32");
+  SB_CHECK_ARG(batch >= 1 && batch <= 65535, "softmax: batch must be in [1, 65535]");
+  if (m == 0 || nnz == 0) return SB_OK;
+  SB_CHECK_ARG(pos && in && out, "softmax: null pointer");
+  dim3 grid((unsigned)ceil_div(m, 8), (unsigned)batch);
+  csr_row_softmax_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((int)m, pos, in, out, scale,
+                                                                 stride);
+  SB_LAUNCH_CHECK("csr_row_softmax_kernel");
+  return SB_OK;
+}
+
+}  // extern "C"

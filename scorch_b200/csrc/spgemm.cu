@@ -1,0 +1,590 @@
+// CSR x CSR SpGEMM (Gustavson) for sm_100a, two phases (symbolic / numeric) like the reference.
+//
+// Rows of A are binned by their product upper bound U_i = sum over the row's entries of the
+// length of the matching B row:
+//   bin 0  U <= 32      one warp per row, 64-slot hash set/accumulator in shared memory
+//   bin 1  U <= 128     one warp per row, 256 slots
+//   bin 2  U <= 1024    one 128-thread CTA per row, 2048 slots
+//   bin 3  U <= 8192    one 512-thread CTA per row, 16384 slots
+//   bin 4  U  > 8192    dense bitmap (+ dense accumulator) of n columns in the workspace, a
+//                       bounded pool of persistent CTAs walks these rows
+// Hash bins: open addressing with atomicCAS on the column key (+ atomicAdd on the value), load
+// factor <= 0.5 by construction.  The numeric phase sorts each row's table in shared memory
+// (bitonic, empty slots = INT_MAX sink to the end) so columns come out ascending like the
+// reference's per-row sort; the dense bin emits columns in bitmap order, which is already
+// ascending.  The structure is the symbolic union: a slot whose value cancels to 0 is kept.
+// Row pointers come from a three-kernel exclusive scan in int64, stored as int32 with an
+// overflow check.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int kBins = 5;
+constexpr int kEmpty = INT_MAX;
+constexpr int kDenseWorkersMax = 296;  // 2 CTAs per SM on a 148-SM part
+constexpr size_t kDenseBudget = (size_t)4 << 30;
+
+// Workspace header (int64 words): [0..4] rows per bin, [5] total nnz of C, [6] dense workers.
+struct WsLayout {
+  long long* hdr;       // 16 int64
+  int* bin_cursor;      // kBins ints (+ padding)
+  int* upper;           // m ints: product upper bound per row (saturating)
+  int* bin_rows;        // kBins * m ints
+  int* row_cnt;         // m ints
+  long long* block_sum; // scan temporaries
+  unsigned* bitmap;     // workers * words
+  void* dense_acc;      // workers * n * sizeof(T)
+  int workers;
+  long long words;      // bitmap words per worker
+  size_t total;
+};
+
+static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+static size_t dtype_size(int dtype) { return (dtype == SB_F64 || dtype == SB_I64) ? 8 : 4; }
+
+static WsLayout ws_layout(void* base, int64_t m, int64_t n, int dtype) {
+  WsLayout w;
+  char* p = static_cast<char*>(base);
+  size_t off = 0;
+  w.hdr = reinterpret_cast<long long*>(p + off); off += align_up(16 * 8);
+  w.bin_cursor = reinterpret_cast<int*>(p + off); off += align_up(16 * 4);
+  w.upper = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4);
+  w.bin_rows = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4 * kBins);
+  w.row_cnt = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4);
+  w.block_sum = reinterpret_cast<long long*>(p + off);
+  off += align_up((size_t)(ceil_div(m > 0 ? m : 1, 4096) + 1) * 8);
+  w.words = (n + 31) / 32;
+  const size_t per_worker = (size_t)w.words * 4 + (size_t)n * dtype_size(dtype);
+  long long workers = per_worker ? (long long)(kDenseBudget / per_worker) : kDenseWorkersMax;
+  if (workers < 1) workers = 1;
+  if (workers > kDenseWorkersMax) workers = kDenseWorkersMax;
+  w.workers = (int)workers;
+  w.bitmap = reinterpret_cast<unsigned*>(p + off); off += align_up((size_t)w.workers * w.words * 4);
+  w.dense_acc = p + off; off += align_up((size_t)w.workers * (size_t)n * dtype_size(dtype));
+  w.total = off;
+  return w;
+}
+
+// ---- binning ---------------------------------------------------------------------------------
+__device__ __forceinline__ int bin_of(int u) {
+  if (u <= 32) return 0;
+  if (u <= 128) return 1;
+  if (u <= 1024) return 2;
+  if (u <= 8192) return 3;
+  return 4;
+}
+
+// 8 lanes per row of A: U_i and the row's bin; rows are appended to their bin's list with one
+// atomic per (warp, bin).  Rows with U = 0 get row_cnt = 0 and join no bin.
+__global__ void __launch_bounds__(256)
+spgemm_bin_kernel(int m, const int* __restrict__ Apos, const int* __restrict__ Acrd,
+                  const int* __restrict__ Bpos, int* __restrict__ upper, int* __restrict__ bin_rows,
+                  int* __restrict__ bin_cursor, int* __restrict__ row_cnt) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = t >> 3;
+  const int l = (int)(t & 7), lane = threadIdx.x & 31;
+  long long u = 0;
+  if (row < m) {
+    const int b = __ldg(Apos + row), e = __ldg(Apos + row + 1);
+    for (int p = b + l; p < e; p += 8) {
+      const int j = ld_stream(Acrd + p);
+      u += __ldg(Bpos + j + 1) - __ldg(Bpos + j);
+    }
+  }
+  u += __shfl_xor_sync(FULL, u, 4);
+  u += __shfl_xor_sync(FULL, u, 2);
+  u += __shfl_xor_sync(FULL, u, 1);
+  const int ui = u > INT_MAX ? INT_MAX : (int)u;
+  const bool owner = (l == 0) && (row < m);
+  int bin = -1;
+  if (owner) {
+    upper[row] = ui;
+    if (ui == 0) row_cnt[row] = 0; else bin = bin_of(ui);
+  }
+#pragma unroll
+  for (int b = 0; b < kBins; b++) {
+    const unsigned mask = __ballot_sync(FULL, bin == b);
+    if (mask == 0) continue;
+    const int leader = __ffs(mask) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(&bin_cursor[b], __popc(mask));
+    base = __shfl_sync(FULL, base, leader);
+    if (bin == b) bin_rows[(long long)b * m + base + __popc(mask & ((1u << lane) - 1))] = (int)row;
+  }
+}
+
+// ---- hash + sort primitives ------------------------------------------------------------------
+template <int S>
+__device__ __forceinline__ int hash_slot(int c) {
+  return (int)(((unsigned)c * 0x9E3779B1u) >> (32 - __builtin_ctz(S)));
+}
+
+// Returns 1 when the key was new.
+template <typename T, int S, bool NUMERIC>
+__device__ __forceinline__ int hash_insert(int* keys, T* vals, int c, T v) {
+  int h = hash_slot<S>(c);
+  while (true) {
+    const int old = atomicCAS(&keys[h], kEmpty, c);
+    if (old == kEmpty || old == c) {
+      if (NUMERIC) atomicAdd(&vals[h], v);
+      return old == kEmpty;
+    }
+    h = (h + 1) & (S - 1);
+  }
+}
+
+template <typename T, int S, int NT, bool WARP_SCOPE>
+__device__ __forceinline__ void bitonic_sort(int* keys, T* vals, int tid) {
+  for (int k = 2; k <= S; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = tid; t < S / 2; t += NT) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+        const int x = i | j;
+        const bool up = (i & k) == 0;
+        const int a = keys[i], b = keys[x];
+        if ((a > b) == up) {
+          keys[i] = b; keys[x] = a;
+          const T va = vals[i]; vals[i] = vals[x]; vals[x] = va;
+        }
+      }
+      if (WARP_SCOPE) __syncwarp(); else __syncthreads();
+    }
+  }
+}
+
+struct CsrIn {
+  const int* Apos; const int* Acrd; const void* Aval;
+  const int* Bpos; const int* Bcrd; const void* Bval;
+};
+
+// One warp per row (bins 0, 1).  The warp's 4 groups of 8 lanes take alternate entries of the A
+// row; a group's lanes span the B row (B rows are short on average).
+template <typename T, int S, bool NUMERIC>
+__global__ void __launch_bounds__(128)
+spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
+                   const int* __restrict__ Cpos, int* __restrict__ Ccrd, T* __restrict__ Cval) {
+  __shared__ int s_keys[4][S];
+  __shared__ T s_vals[4][NUMERIC ? S : 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + warp;
+  if (r >= nrows) return;
+  const int i = __ldg(rows + r);
+  int* keys = s_keys[warp];
+  T* vals = s_vals[warp];
+  for (int t = lane; t < S; t += 32) {
+    keys[t] = kEmpty;
+    if (NUMERIC) vals[t] = T(0);
+  }
+  __syncwarp();
+  const T* Aval = static_cast<const T*>(in.Aval);
+  const T* Bval = static_cast<const T*>(in.Bval);
+  const int g = lane >> 3, l = lane & 7;
+  const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
+  int fresh = 0;
+  for (int pa = ab + g; pa < ae; pa += 4) {
+    const int j = __ldg(in.Acrd + pa);
+    T a = T(0);
+    if (NUMERIC) a = Aval[pa];
+    const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
+    for (int pb = bb + l; pb < be; pb += 8) {
+      const int c = __ldg(in.Bcrd + pb);
+      T v = T(0);
+      if (NUMERIC) v = a * Bval[pb];
+      fresh += hash_insert<T, S, NUMERIC>(keys, vals, c, v);
+    }
+  }
+  __syncwarp();
+  if (!NUMERIC) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) fresh += __shfl_xor_sync(FULL, fresh, o);
+    if (lane == 0) row_cnt[i] = fresh;
+  } else {
+    bitonic_sort<T, S, 32, true>(keys, vals, lane);
+    const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
+    for (int t = lane; t < cnt; t += 32) {
+      Ccrd[base + t] = keys[t];
+      Cval[base + t] = vals[t];
+    }
+  }
+}
+
+// One CTA per row (bins 2, 3): warps take alternate entries of the A row, lanes span the B row.
+template <typename T, int S, int NT, bool NUMERIC>
+__global__ void __launch_bounds__(NT)
+spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
+                  const int* __restrict__ Cpos, int* __restrict__ Ccrd, T* __restrict__ Cval) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* vals = reinterpret_cast<T*>(smem_raw);                       // S values (numeric only)
+  int* keys = reinterpret_cast<int*>(smem_raw + (NUMERIC ? sizeof(T) * S : 0));
+  __shared__ int s_fresh;
+  const int r = blockIdx.x;
+  if (r >= nrows) return;
+  const int i = __ldg(rows + r);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int t = tid; t < S; t += NT) {
+    keys[t] = kEmpty;
+    if (NUMERIC) vals[t] = T(0);
+  }
+  if (tid == 0) s_fresh = 0;
+  __syncthreads();
+  const T* Aval = static_cast<const T*>(in.Aval);
+  const T* Bval = static_cast<const T*>(in.Bval);
+  const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
+  int fresh = 0;
+  for (int pa = ab + warp; pa < ae; pa += NT / 32) {
+    const int j = __ldg(in.Acrd + pa);
+    T a = T(0);
+    if (NUMERIC) a = Aval[pa];
+    const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
+    for (int pb = bb + lane; pb < be; pb += 32) {
+      const int c = __ldg(in.Bcrd + pb);
+      T v = T(0);
+      if (NUMERIC) v = a * Bval[pb];
+      fresh += hash_insert<T, S, NUMERIC>(keys, vals, c, v);
+    }
+  }
+  if (!NUMERIC) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) fresh += __shfl_xor_sync(FULL, fresh, o);
+    if (lane == 0 && fresh) atomicAdd(&s_fresh, fresh);
+    __syncthreads();
+    if (tid == 0) row_cnt[i] = s_fresh;
+  } else {
+    __syncthreads();
+    bitonic_sort<T, S, NT, false>(keys, vals, tid);
+    const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
+    for (int t = tid; t < cnt; t += NT) {
+      Ccrd[base + t] = keys[t];
+      Cval[base + t] = vals[t];
+    }
+  }
+}
+
+// Bin 4: persistent CTAs, each owning one bitmap (+ accumulator) of n columns in the workspace.
+// Both stay all-zero between rows: every set bit / touched sum is cleared while it is emitted.
+template <typename T, bool NUMERIC>
+__global__ void __launch_bounds__(256)
+spgemm_dense_kernel(const int* __restrict__ rows, int nrows, CsrIn in, long long words,
+                    unsigned* __restrict__ bitmap_all, T* __restrict__ acc_all, long long n,
+                    int* __restrict__ row_cnt, const int* __restrict__ Cpos,
+                    int* __restrict__ Ccrd, T* __restrict__ Cval) {
+  __shared__ int s_warp[8];
+  __shared__ int s_base;
+  unsigned* bitmap = bitmap_all + (long long)blockIdx.x * words;
+  T* acc = NUMERIC ? acc_all + (long long)blockIdx.x * n : nullptr;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const T* Aval = static_cast<const T*>(in.Aval);
+  const T* Bval = static_cast<const T*>(in.Bval);
+  for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
+    const int i = __ldg(rows + r);
+    const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
+    for (int pa = ab + warp; pa < ae; pa += 8) {
+      const int j = __ldg(in.Acrd + pa);
+      T a = T(0);
+      if (NUMERIC) a = Aval[pa];
+      const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
+      for (int pb = bb + lane; pb < be; pb += 32) {
+        const int c = __ldg(in.Bcrd + pb);
+        if (NUMERIC) atomicAdd(&acc[c], a * Bval[pb]);
+        atomicOr(&bitmap[c >> 5], 1u << (c & 31));
+      }
+    }
+    __syncthreads();
+    // walk the bitmap in ascending order, 256 words per step
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    const int out0 = NUMERIC ? __ldg(Cpos + i) : 0;
+    for (long long w0 = 0; w0 < words; w0 += 256) {
+      const long long w = w0 + tid;
+      unsigned bits = 0;
+      if (w < words) {
+        bits = __ldcg(bitmap + w);  // the bits were set by L2 atomics: do not trust L1
+        if (bits) bitmap[w] = 0;
+      }
+      const int cnt = __popc(bits);
+      // block-wide exclusive scan of cnt
+      int incl = cnt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(FULL, incl, o);
+        if (lane >= o) incl += y;
+      }
+      if (lane == 31) s_warp[warp] = incl;
+      __syncthreads();
+      int warp_off = 0, step_total = 0;
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        const int v = s_warp[q];
+        if (q < warp) warp_off += v;
+        step_total += v;
+      }
+      const int base = s_base;
+      if (NUMERIC && bits) {
+        int o = out0 + base + warp_off + incl - cnt;
+        while (bits) {
+          const int bit = __ffs(bits) - 1;
+          bits &= bits - 1;
+          const long long c = w * 32 + bit;
+          Ccrd[o] = (int)c;
+          Cval[o] = __ldcg(acc + c);
+          acc[c] = T(0);
+          o++;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) s_base = base + step_total;
+      __syncthreads();
+    }
+    if (!NUMERIC && tid == 0) row_cnt[i] = s_base;
+    __syncthreads();
+  }
+}
+
+// ---- exclusive scan of row counts (int64 accumulate, int32 store) ------------------------------
+constexpr int kScanTile = 4096;
+
+__global__ void __launch_bounds__(1024)
+scan_reduce_kernel(int m, const int* __restrict__ cnt, long long* __restrict__ block_sum) {
+  __shared__ long long s[32];
+  const long long base = (long long)blockIdx.x * kScanTile;
+  long long v = 0;
+  for (int q = 0; q < 4; q++) {
+    const long long i = base + q * 1024 + threadIdx.x;
+    if (i < m) v += cnt[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    v = s[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    if (threadIdx.x == 0) block_sum[blockIdx.x] = v;
+  }
+}
+
+__global__ void scan_blocks_kernel(int nb, long long* block_sum, long long* hdr_total) {
+  // single thread block, sequential over at most a few thousand tiles
+  if (threadIdx.x == 0) {
+    long long run = 0;
+    for (int b = 0; b < nb; b++) {
+      const long long v = block_sum[b];
+      block_sum[b] = run;
+      run += v;
+    }
+    *hdr_total = run;
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+scan_write_kernel(int m, const int* __restrict__ cnt, const long long* __restrict__ block_sum,
+                  int* __restrict__ Cpos) {
+  __shared__ long long s[32];
+  const long long base = (long long)blockIdx.x * kScanTile;
+  // each thread owns 4 consecutive rows
+  const long long i0 = base + (long long)threadIdx.x * 4;
+  int c[4];
+  long long mine = 0;
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    c[q] = (i0 + q < m) ? cnt[i0 + q] : 0;
+    mine += c[q];
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  long long incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const long long y = __shfl_up_sync(FULL, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) s[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    long long v = s[lane];
+    long long iv = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long y = __shfl_up_sync(FULL, iv, o);
+      if (lane >= o) iv += y;
+    }
+    s[lane] = iv - v;  // exclusive over warps
+  }
+  __syncthreads();
+  long long run = block_sum[blockIdx.x] + s[warp] + incl - mine;
+  if (blockIdx.x == 0 && threadIdx.x == 0) Cpos[0] = 0;
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    run += c[q];
+    if (i0 + q < m) Cpos[i0 + q + 1] = (int)run;
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+template <typename T, bool NUMERIC>
+static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, int64_t n,
+                       const CsrIn& in, const int* Cpos, int* Ccrd, T* Cval, cudaStream_t st) {
+  const int* rows0 = w.bin_rows;
+  if (counts[0] > 0) {
+    spgemm_warp_kernel<T, 64, NUMERIC><<<(unsigned)ceil_div(counts[0], 4), 128, 0, st>>>(
+        rows0, (int)counts[0], in, w.row_cnt, Cpos, Ccrd, Cval);
+    SB_LAUNCH_CHECK("spgemm_warp_kernel<64>");
+  }
+  if (counts[1] > 0) {
+    spgemm_warp_kernel<T, 256, NUMERIC><<<(unsigned)ceil_div(counts[1], 4), 128, 0, st>>>(
+        rows0 + m, (int)counts[1], in, w.row_cnt, Cpos, Ccrd, Cval);
+    SB_LAUNCH_CHECK("spgemm_warp_kernel<256>");
+  }
+  if (counts[2] > 0) {
+    constexpr int S = 2048;
+    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);
+    auto k = spgemm_cta_kernel<T, S, 128, NUMERIC>;
+    SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<(unsigned)counts[2], 128, smem, st>>>(rows0 + 2 * m, (int)counts[2], in, w.row_cnt, Cpos,
+                                             Ccrd, Cval);
+    SB_LAUNCH_CHECK("spgemm_cta_kernel<2048>");
+  }
+  if (counts[3] > 0) {
+    constexpr int S = 16384;
+    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);
+    auto k = spgemm_cta_kernel<T, S, 512, NUMERIC>;
+    SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<(unsigned)counts[3], 512, smem, st>>>(rows0 + 3 * m, (int)counts[3], in, w.row_cnt, Cpos,
+                                             Ccrd, Cval);
+    SB_LAUNCH_CHECK("spgemm_cta_kernel<16384>");
+  }
+  if (counts[4] > 0) {
+    const int workers = (int)(counts[4] < w.workers ? counts[4] : w.workers);
+    spgemm_dense_kernel<T, NUMERIC><<<workers, 256, 0, st>>>(
+        rows0 + 4 * m, (int)counts[4], in, w.words, w.bitmap, static_cast<T*>(w.dense_acc),
+        (long long)n, w.row_cnt, Cpos, Ccrd, Cval);
+    SB_LAUNCH_CHECK("spgemm_dense_kernel");
+  }
+  return SB_OK;
+}
+
+static int check_spgemm(int64_t m, int64_t kb, int64_t n, const void* Apos, const void* Bpos,
+                        void* ws, size_t ws_bytes, int dtype) {
+  SB_CHECK_ARG(m >= 0 && kb >= 0 && n >= 0, "spgemm: negative size");
+  SB_CHECK_ARG(m < INT32_MAX / 8 && kb < INT32_MAX && n < INT32_MAX - 1,
+               "spgemm: dimension exceeds the supported int32 range");
+  SB_CHECK_ARG(Apos && Bpos, "spgemm: null row pointers");
+  SB_CHECK_ARG(ws && aligned16(ws), "spgemm: workspace is null or misaligned");
+  (void)dtype;
+  const size_t need = sb_spgemm_workspace_bytes(m, n, SB_F32);  // the same for every dtype
+  if (ws_bytes < need)
+    return fail(SB_ERR_WORKSPACE, "spgemm: workspace has %zu bytes, needs %zu", ws_bytes, need);
+  return SB_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+size_t sb_spgemm_workspace_bytes(int64_t m, int64_t n, int dtype) {
+  if (m < 0) m = 0;
+  if (n < 0) n = 0;
+  // One size for all dtypes (the symbolic phase does not know the numeric dtype): the largest
+  // of the per-dtype layouts.
+  (void)dtype;
+  const size_t a = ws_layout(nullptr, m, n, SB_F32).total;
+  const size_t b = ws_layout(nullptr, m, n, SB_F64).total;
+  return a > b ? a : b;
+}
+
+int sb_spgemm_symbolic(int64_t m, int64_t kb, int64_t n, const int32_t* Apos, const int32_t* Acrd,
+                       const int32_t* Bpos, const int32_t* Bcrd, int32_t* Cpos,
+                       int64_t* total_nnz_host, void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_spgemm(m, kb, n, Apos, Bpos, ws, ws_bytes, SB_F32);
+  if (rc != SB_OK) return rc;
+  SB_CHECK_ARG(Cpos && total_nnz_host, "spgemm_symbolic: null output");
+  cudaStream_t st = (cudaStream_t)stream;
+  // the symbolic phase only needs the bitmaps; lay the workspace out for the smallest dtype so
+  // that any numeric dtype (whose layout is recomputed there) fits the caller's buffer
+  WsLayout w = ws_layout(ws, m, n, SB_F32);
+  *total_nnz_host = 0;
+  SB_CUDA(cudaMemsetAsync(w.hdr, 0, 16 * 8, st));
+  SB_CUDA(cudaMemsetAsync(w.bin_cursor, 0, 16 * 4, st));
+  if (m == 0) {
+    SB_CUDA(cudaMemsetAsync(Cpos, 0, 4, st));
+    SB_CUDA(cudaStreamSynchronize(st));
+    return SB_OK;
+  }
+  spgemm_bin_kernel<<<(unsigned)ceil_div(m * 8, 256), 256, 0, st>>>(
+      (int)m, Apos, Acrd, Bpos, w.upper, w.bin_rows, w.bin_cursor, w.row_cnt);
+  SB_LAUNCH_CHECK("spgemm_bin_kernel");
+  int cursors[kBins];
+  SB_CUDA(cudaMemcpyAsync(cursors, w.bin_cursor, sizeof(cursors), cudaMemcpyDeviceToHost, st));
+  SB_CUDA(cudaStreamSynchronize(st));
+  long long counts[kBins];
+  for (int b = 0; b < kBins; b++) counts[b] = cursors[b];
+  if (counts[4] > 0) SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
+  CsrIn in{Apos, Acrd, nullptr, Bpos, Bcrd, nullptr};
+  rc = launch_bins<float, false>(w, counts, m, n, in, nullptr, nullptr, nullptr, st);
+  if (rc != SB_OK) return rc;
+  const int nb = (int)ceil_div(m, kScanTile);
+  scan_reduce_kernel<<<nb, 1024, 0, st>>>((int)m, w.row_cnt, w.block_sum);
+  SB_LAUNCH_CHECK("scan_reduce_kernel");
+  scan_blocks_kernel<<<1, 32, 0, st>>>(nb, w.block_sum, w.hdr + 5);
+  SB_LAUNCH_CHECK("scan_blocks_kernel");
+  scan_write_kernel<<<nb, 1024, 0, st>>>((int)m, w.row_cnt, w.block_sum, Cpos);
+  SB_LAUNCH_CHECK("scan_write_kernel");
+  // keep the bin sizes in the workspace header for the numeric phase
+  SB_CUDA(cudaMemcpyAsync(w.hdr, counts, sizeof(counts), cudaMemcpyHostToDevice, st));
+  long long total = 0;
+  SB_CUDA(cudaMemcpyAsync(&total, w.hdr + 5, 8, cudaMemcpyDeviceToHost, st));
+  SB_CUDA(cudaStreamSynchronize(st));
+  *total_nnz_host = total;
+  if (total > INT32_MAX)
+    return fail(SB_ERR_OVERFLOW, "spgemm: the product has %lld stored entries, which does not fit "
+                "the int32 row pointers", total);
+  return SB_OK;
+}
+
+int sb_spgemm_numeric(int dtype, int64_t m, int64_t kb, int64_t n, const int32_t* Apos,
+                      const int32_t* Acrd, const void* Aval, const int32_t* Bpos,
+                      const int32_t* Bcrd, const void* Bval, const int32_t* Cpos, int32_t* Ccrd,
+                      void* Cval, void* ws, size_t ws_bytes, void* stream) {
+  SB_CHECK_ARG(dtype >= SB_F32 && dtype <= SB_I64, "spgemm_numeric: unknown dtype");
+  int rc = check_spgemm(m, kb, n, Apos, Bpos, ws, ws_bytes, dtype);
+  if (rc != SB_OK) return rc;
+  SB_CHECK_ARG(Cpos, "spgemm_numeric: Cpos is null");
+  if (m == 0) return SB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the row bins sit at dtype-independent offsets; the dense area is re-laid-out for `dtype`
+  WsLayout w = ws_layout(ws, m, n, dtype);
+  long long counts[kBins];
+  SB_CUDA(cudaMemcpyAsync(counts, w.hdr, sizeof(counts), cudaMemcpyDeviceToHost, st));
+  SB_CUDA(cudaStreamSynchronize(st));
+  long long binned = 0;
+  for (int b = 0; b < kBins; b++) {
+    SB_CHECK_ARG(counts[b] >= 0 && counts[b] <= m, "spgemm_numeric: workspace does not hold the "
+                 "bins of a symbolic call");
+    binned += counts[b];
+  }
+  SB_CHECK_ARG(binned <= m, "spgemm_numeric: workspace does not hold the bins of a symbolic call");
+  if (binned == 0) return SB_OK;
+  SB_CHECK_ARG(Ccrd && Cval && Aval && Bval, "spgemm_numeric: null pointer");
+  if (counts[4] > 0) {
+    SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
+    SB_CUDA(cudaMemsetAsync(w.dense_acc, 0, (size_t)w.workers * (size_t)n * dtype_size(dtype), st));
+  }
+  CsrIn in{Apos, Acrd, Aval, Bpos, Bcrd, Bval};
+  switch (dtype) {
+    case SB_F32:
+      return launch_bins<float, true>(w, counts, m, n, in, Cpos, Ccrd, (float*)Cval, st);
+    case SB_F64:
+      return launch_bins<double, true>(w, counts, m, n, in, Cpos, Ccrd, (double*)Cval, st);
+    case SB_I32:
+      return launch_bins<unsigned int, true>(w, counts, m, n, in, Cpos, Ccrd, (unsigned int*)Cval, st);
+    default:
+      return launch_bins<unsigned long long, true>(w, counts, m, n, in, Cpos, Ccrd,
+                                                   (unsigned long long*)Cval, st);
+  }
+}
+
+}  // extern "C"

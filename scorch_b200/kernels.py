@@ -1,0 +1,290 @@
+"""Device-tensor front end of the C ABI: every function takes CUDA torch tensors (torch is used
+for device memory and streams only) and launches the sm_100a kernels through ``_lib``.
+
+No function here computes on the CPU; CPU tensors are rejected (the host-tensor convenience
+path lives in ``scorch_ops``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import SB_F32, SB_F64, SB_I32, SB_I64, check
+
+_DTYPE_CODE = {torch.float32: SB_F32, torch.float64: SB_F64, torch.int32: SB_I32, torch.int64: SB_I64}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class CsrPlan:
+    """Heavy-row plan of one CSR matrix (depends on ``pos`` only); see include/scorch_b200.h."""
+
+    def __init__(self, pos: torch.Tensor, nnz: int):
+        pos = _dev(pos, torch.int32, "pos")
+        self.m = pos.numel() - 1
+        self.nnz = int(nnz)
+        L = _lib.lib()
+        nbytes = L.sb_csr_plan_bytes(self.m, self.nnz)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=pos.device)
+        with torch.cuda.device(pos.device):
+            check(L.sb_csr_plan_build(self.m, self.nnz, pos.data_ptr(), self.buf.data_ptr(), nbytes,
+                                      _stream()))
+            h, s = C.c_int64(0), C.c_int64(0)
+            check(L.sb_csr_plan_counts(self.buf.data_ptr(), C.byref(h), C.byref(s), _stream()))
+        self.heavy_rows, self.segments = int(h.value), int(s.value)
+        self._scratch: Optional[torch.Tensor] = None
+
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=self.buf.device)
+        return self._scratch
+
+
+def plan_for(pos: torch.Tensor, nnz: int) -> CsrPlan:
+    """Plan cached on the ``pos`` tensor object (rebuilt if the tensor was written in place)."""
+    cached = getattr(pos, "_sb_plan", None)
+    if cached is not None and cached[0] == pos._version and cached[1].nnz == nnz:
+        return cached[1]
+    plan = CsrPlan(pos, nnz)
+    try:
+        pos._sb_plan = (pos._version, plan)
+    except Exception:  # pragma: no cover - tensors always accept attributes
+        pass
+    return plan
+
+
+def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[CsrPlan] = None,
+             out: Optional[torch.Tensor] = None, n: Optional[int] = None) -> torch.Tensor:
+    """C = act(bias + A @ B) for CSR A.  ``B`` is (n, k) or (batch, n, k); ``val`` is (nnz,) —
+    shared by all batch items — or (batch, nnz).  Returns (m, k) or (batch, m, k)."""
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    m, nnz = pos.numel() - 1, crd.numel()
+    if val.dtype != torch.float32:
+        return _spmm_typed(pos, crd, val, B, n)
+    val = _dev(val, torch.float32, "val")
+    B = _dev(B, torch.float32, "B")
+    batched = B.dim() == 3
+    batch = B.shape[0] if batched else 1
+    nb, k = B.shape[-2], B.shape[-1]
+    if val.dim() == 2:
+        if val.shape[0] != batch or val.shape[1] != nnz:
+            raise ValueError("val must be (nnz,) or (batch, nnz)")
+        stride_val = nnz
+    else:
+        if val.numel() != nnz:
+            raise ValueError("val and crd differ in length")
+        stride_val = 0
+    if bias is not None:
+        bias = _dev(bias, torch.float32, "bias")
+        if bias.numel() != k:
+            raise ValueError("bias must have k elements")
+    shape = (batch, m, k) if batched else (m, k)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=B.device)
+    else:
+        out = _dev(out, torch.float32, "out")
+        if tuple(out.shape) != shape:
+            raise ValueError(f"out must have shape {shape}")
+    if plan is None:
+        plan = plan_for(pos, nnz)
+    L = _lib.lib()
+    sbytes = L.sb_spmm_csr_scratch_bytes(plan.segments, k, batch)
+    scratch = plan.scratch(sbytes) if sbytes else None
+    with torch.cuda.device(B.device):
+        check(L.sb_spmm_csr_f32(m, nb if n is None else n, k, nnz, pos.data_ptr(), crd.data_ptr(),
+                                val.data_ptr(), B.data_ptr(), k, _ptr(bias), int(bool(relu)),
+                                out.data_ptr(), k, batch, stride_val, nb * k, m * k,
+                                plan.buf.data_ptr(), plan.segments, _ptr(scratch), sbytes,
+                                _stream()))
+    return out
+
+
+def _spmm_typed(pos, crd, val, B, n):
+    code = _DTYPE_CODE.get(val.dtype)
+    if code is None:
+        raise TypeError(f"unsupported value dtype {val.dtype}")
+    val = _dev(val, val.dtype, "val")
+    B = _dev(B, val.dtype, "B")
+    if B.dim() != 2:
+        raise ValueError("typed SpMM takes a 2-D dense operand")
+    m, nnz, k = pos.numel() - 1, crd.numel(), B.shape[1]
+    out = torch.empty((m, k), dtype=val.dtype, device=B.device)
+    with torch.cuda.device(B.device):
+        check(_lib.lib().sb_spmm_csr_typed(code, m, B.shape[0] if n is None else n, k, nnz,
+                                           pos.data_ptr(), crd.data_ptr(), val.data_ptr(),
+                                           B.data_ptr(), k, out.data_ptr(), k, _stream()))
+    return out
+
+
+def spmv_csr(pos, crd, val, x, plan: Optional[CsrPlan] = None) -> torch.Tensor:
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    m, nnz = pos.numel() - 1, crd.numel()
+    code = _DTYPE_CODE.get(val.dtype)
+    if code is None:
+        raise TypeError(f"unsupported value dtype {val.dtype}")
+    val = _dev(val, val.dtype, "val")
+    x = _dev(x, val.dtype, "x")
+    y = torch.empty(m, dtype=val.dtype, device=x.device)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        if code != SB_F32:
+            check(L.sb_spmv_csr_typed(code, m, x.numel(), nnz, pos.data_ptr(), crd.data_ptr(),
+                                      val.data_ptr(), x.data_ptr(), y.data_ptr(), _stream()))
+            return y
+        if plan is None:
+            plan = plan_for(pos, nnz)
+        sbytes = L.sb_spmv_csr_scratch_bytes(plan.segments)
+        scratch = plan.scratch(sbytes) if sbytes else None
+        check(L.sb_spmv_csr_f32(m, x.numel(), nnz, pos.data_ptr(), crd.data_ptr(), val.data_ptr(),
+                                x.data_ptr(), y.data_ptr(), plan.buf.data_ptr(), plan.segments,
+                                _ptr(scratch), sbytes, _stream()))
+    return y
+
+
+def _qk(Q, K):
+    Q = _dev(Q, torch.float32, "Q")
+    K = _dev(K, torch.float32, "K")
+    if Q.dim() != K.dim() or Q.dim() not in (2, 3) or Q.shape[-1] != K.shape[-1]:
+        raise ValueError("Q and K must be (rows, d) or (batch, rows, d) with equal d")
+    batch = Q.shape[0] if Q.dim() == 3 else 1
+    if K.dim() == 3 and K.shape[0] != batch:
+        raise ValueError("Q and K differ in batch size")
+    return Q, K, batch
+
+
+def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False):
+    """out[p] = mask_val[p] * <Q[i_p], K[j_p]> over the entries of a CSR mask, entry order kept.
+    Returns values (nnz,) or (batch, nnz); with ``want_coords`` also fresh int32 (row, col)."""
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    Q, K, batch = _qk(Q, K)
+    m, nnz, d = pos.numel() - 1, crd.numel(), Q.shape[-1]
+    if mask_val is not None:
+        mask_val = _dev(mask_val, torch.float32, "mask_val")
+    out = torch.empty((batch, nnz) if Q.dim() == 3 else (nnz,), dtype=torch.float32, device=Q.device)
+    row = col = None
+    if want_coords:
+        row = torch.empty(nnz, dtype=torch.int32, device=Q.device)
+        col = torch.empty(nnz, dtype=torch.int32, device=Q.device)
+    with torch.cuda.device(Q.device):
+        check(_lib.lib().sb_sddmm_csr_f32(m, K.shape[-2], d, nnz, pos.data_ptr(), crd.data_ptr(),
+                                          _ptr(mask_val), Q.data_ptr(), d, K.data_ptr(), d,
+                                          out.data_ptr(), _ptr(row), _ptr(col), batch,
+                                          Q.shape[-2] * d, K.shape[-2] * d, nnz, _stream()))
+    return (out, row, col) if want_coords else out
+
+
+def sddmm_coo(row, col, mask_val, Q, K):
+    row = _dev(row, torch.int32, "row")
+    col = _dev(col, torch.int32, "col")
+    Q, K, batch = _qk(Q, K)
+    nnz, d = col.numel(), Q.shape[-1]
+    if mask_val is not None:
+        mask_val = _dev(mask_val, torch.float32, "mask_val")
+    out = torch.empty((batch, nnz) if Q.dim() == 3 else (nnz,), dtype=torch.float32, device=Q.device)
+    with torch.cuda.device(Q.device):
+        check(_lib.lib().sb_sddmm_coo_f32(Q.shape[-2], K.shape[-2], d, nnz, row.data_ptr(),
+                                          col.data_ptr(), _ptr(mask_val), Q.data_ptr(), d,
+                                          K.data_ptr(), d, out.data_ptr(), batch, Q.shape[-2] * d,
+                                          K.shape[-2] * d, nnz, _stream()))
+    return out
+
+
+def csr_row_softmax(pos, val, scale: float = 1.0, out: Optional[torch.Tensor] = None):
+    pos = _dev(pos, torch.int32, "pos")
+    val = _dev(val, torch.float32, "val")
+    m = pos.numel() - 1
+    nnz = val.shape[-1]
+    batch = val.shape[0] if val.dim() == 2 else 1
+    if out is None:
+        out = torch.empty_like(val)
+    with torch.cuda.device(val.device):
+        check(_lib.lib().sb_csr_row_softmax_f32(m, nnz, pos.data_ptr(), val.data_ptr(),
+                                                out.data_ptr(), float(scale), batch, nnz, _stream()))
+    return out
+
+
+def spgemm_csr(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n: int, timings: Optional[dict] = None
+               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """C = A @ B for CSR operands.  Returns (Cpos int32, Ccrd int32 ascending per row, Cval)."""
+    Apos, Acrd = _dev(Apos, torch.int32, "Apos"), _dev(Acrd, torch.int32, "Acrd")
+    Bpos, Bcrd = _dev(Bpos, torch.int32, "Bpos"), _dev(Bcrd, torch.int32, "Bcrd")
+    code = _DTYPE_CODE.get(Aval.dtype)
+    if code is None or Bval.dtype != Aval.dtype:
+        raise TypeError("SpGEMM operands must share one of f32/f64/i32/i64")
+    Aval, Bval = _dev(Aval, Aval.dtype, "Aval"), _dev(Bval, Aval.dtype, "Bval")
+    m, kb = Apos.numel() - 1, Bpos.numel() - 1
+    L = _lib.lib()
+    dev = Aval.device
+    with torch.cuda.device(dev):
+        wbytes = L.sb_spgemm_workspace_bytes(m, n, code)
+        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        Cpos = torch.empty(m + 1, dtype=torch.int32, device=dev)
+        total = C.c_int64(0)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if timings is not None else None
+        if ev:
+            ev[0].record()
+        check(L.sb_spgemm_symbolic(m, kb, n, Apos.data_ptr(), Acrd.data_ptr(), Bpos.data_ptr(),
+                                   Bcrd.data_ptr(), Cpos.data_ptr(), C.byref(total),
+                                   ws.data_ptr(), wbytes, _stream()))
+        if ev:
+            ev[1].record()
+        Ccrd = torch.empty(total.value, dtype=torch.int32, device=dev)
+        Cval = torch.empty(total.value, dtype=Aval.dtype, device=dev)
+        check(L.sb_spgemm_numeric(code, m, kb, n, Apos.data_ptr(), Acrd.data_ptr(), Aval.data_ptr(),
+                                  Bpos.data_ptr(), Bcrd.data_ptr(), Bval.data_ptr(),
+                                  Cpos.data_ptr(), Ccrd.data_ptr(), Cval.data_ptr(), ws.data_ptr(),
+                                  wbytes, _stream()))
+        if ev:
+            ev[2].record()
+            ev[2].synchronize()
+            timings["symbolic_ms"] = ev[0].elapsed_time(ev[1])
+            timings["numeric_ms"] = ev[1].elapsed_time(ev[2])
+    return Cpos, Ccrd, Cval
+
+
+def partition_rows_by_nnz(pos: torch.Tensor, parts: int) -> list:
+    """Row bounds [r_0=0, r_1, ..., r_parts=m] of nnz-balanced contiguous row blocks."""
+    pos = _dev(pos, torch.int32, "pos")
+    out = torch.empty(parts + 1, dtype=torch.int64, device=pos.device)
+    with torch.cuda.device(pos.device):
+        check(_lib.lib().sb_partition_rows_by_nnz(pos.numel() - 1, pos.data_ptr(), parts,
+                                                  out.data_ptr(), _stream()))
+    return out.cpu().tolist()
+
+
+def coo_rows_to_csr_pos(row_sorted: torch.Tensor, m: int) -> torch.Tensor:
+    row_sorted = _dev(row_sorted, torch.int32, "row")
+    pos = torch.empty(m + 1, dtype=torch.int32, device=row_sorted.device)
+    with torch.cuda.device(row_sorted.device):
+        check(_lib.lib().sb_coo_rows_to_csr_pos(m, row_sorted.numel(), row_sorted.data_ptr(),
+                                                pos.data_ptr(), _stream()))
+    return pos
+
+
+def csr_pos_to_coo_rows(pos: torch.Tensor, nnz: int) -> torch.Tensor:
+    pos = _dev(pos, torch.int32, "pos")
+    row = torch.empty(nnz, dtype=torch.int32, device=pos.device)
+    with torch.cuda.device(pos.device):
+        check(_lib.lib().sb_csr_pos_to_coo_rows(pos.numel() - 1, nnz, pos.data_ptr(),
+                                                row.data_ptr(), _stream()))
+    return row

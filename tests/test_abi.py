@@ -1,0 +1,68 @@
+"""The C-ABI library loads and exports every symbol include/scorch_b200.h declares; host-side
+argument validation returns error codes (no GPU work is launched here)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+from conftest import ROOT
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "scorch_b200.h")).read()
+    return sorted(set(re.findall(r"SB_API\s+[\w\s\*]+?\b(sb_\w+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported_and_bound(sb_lib):
+    from scorch_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(sb_lib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_version_and_status_strings(sb_lib):
+    assert sb_lib.sb_abi_version() == 1
+    assert sb_lib.sb_status_string(0) == b"ok"
+    assert b"overflow" in sb_lib.sb_status_string(3)
+
+
+def test_size_queries_are_pure_host_functions(sb_lib):
+    from scorch_b200._lib import HEAVY_ROW_NNZ
+    assert sb_lib.sb_csr_plan_bytes(10, 0) >= 32
+    nnz = 10 * HEAVY_ROW_NNZ
+    assert sb_lib.sb_csr_plan_max_segments(nnz) >= 10
+    assert sb_lib.sb_spmm_csr_scratch_bytes(7, 64, 2) == 7 * 64 * 2 * 4
+    assert sb_lib.sb_spmm_csr_scratch_bytes(0, 64, 1) == 0
+    assert sb_lib.sb_spmv_csr_scratch_bytes(5) == 20
+    small = sb_lib.sb_spgemm_workspace_bytes(100, 100, 0)
+    big = sb_lib.sb_spgemm_workspace_bytes(100, 1 << 20, 0)
+    assert 0 < small < big
+    # the dense-row area is capped, so a huge column count cannot ask for unbounded memory
+    assert sb_lib.sb_spgemm_workspace_bytes(1000, 1 << 30, 1) < (20 << 30)
+
+
+def test_argument_validation_returns_codes_without_launching(sb_lib):
+    from scorch_b200._lib import ScorchB200Error, check
+    import pytest
+    one = C.c_void_p(16)  # never dereferenced: validation fails first
+    rc = sb_lib.sb_spmm_csr_f32(-1, 4, 4, 0, one, one, one, one, 4, None, 0, one, 4, 1, 0, 0, 0,
+                                None, 0, None, 0, None)
+    assert rc == 1 and b"negative" in sb_lib.sb_last_error()
+    rc = sb_lib.sb_spmm_csr_f32(4, 4, 8, 0, one, one, one, one, 4, None, 0, one, 8, 1, 0, 0, 0,
+                                None, 0, None, 0, None)
+    assert rc == 1 and b"leading dimension" in sb_lib.sb_last_error()
+    # nnz beyond int32: the reference would wrap (csrc/kernels.h:520); here it is an error code
+    rc = sb_lib.sb_sddmm_coo_f32(4, 4, 4, 1 << 31, one, one, None, one, 4, one, 4, one, 1, 0, 0, 0, None)
+    assert rc == 3
+    rc = sb_lib.sb_spmv_csr_typed(9, 4, 4, 0, one, one, one, one, one, None)
+    assert rc == 5 or rc == 1
+    rc = sb_lib.sb_csr_plan_build(4, 4, one, one, 8, None)
+    assert rc == 4 and b"needs" in sb_lib.sb_last_error()
+    with pytest.raises(ScorchB200Error) as e:
+        check(sb_lib.sb_spgemm_symbolic(4, 4, 4, one, one, one, one, one, C.pointer(C.c_int64(0)),
+                                        one, 16, None))
+    assert e.value.status == 4
