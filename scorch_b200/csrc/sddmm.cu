@@ -1,13 +1,13 @@
 // SDDMM (sampled dense-dense product) over the stored entries of a CSR or COO mask, and the row
 // softmax over CSR values that sits between SDDMM and SpMM in sparse attention.
 //
-// SDDMM work split: the entry list is cut into chunks of 32 consecutive entries, one warp per
-// chunk, so the split is balanced by nnz whatever the row lengths are.  The warp reads the
-// chunk's column ids / mask values with one coalesced load, finds each entry's row (one binary
-// search per warp plus a short per-lane refinement when a chunk crosses rows), then G lanes
-// compute one dot product with 128-bit loads of the K row and a shuffle tree; the Q row stays in
-// registers while consecutive entries share it.  Results are written back one coalesced line
-// per chunk.
+// SDDMM work split: the entry list is cut into spans of 8 x 32 consecutive entries, one warp per
+// span, so the split is balanced by nnz whatever the row lengths are.  Per 32-entry chunk the
+// warp reads the column ids / mask values with one coalesced load and finds each entry's row
+// (one binary search per span, a short forward walk per chunk, a per-lane refinement only when
+// a chunk crosses rows); then G lanes compute one dot product with 128-bit loads of the K row
+// and a shuffle tree, and the Q row stays in registers while consecutive entries share it.
+// Results are written back one coalesced line per chunk.
 #include <math.h>
 
 #include "common.cuh"
@@ -34,96 +34,105 @@ struct SddmmArgs {
   long long stride_q, stride_k, stride_out;
 };
 
-// Row ids of the 32 entries [p0, p0+32) of a CSR matrix, one per lane.
-__device__ __forceinline__ int chunk_rows(const int* __restrict__ pos, int m, long long p0,
-                                          int cnt, int lane) {
-  // warp-uniform: row of the first entry
-  const int r0 = row_of_entry(pos, 0, m, (int)p0);
-  int r = r0;
-  const int last = (int)p0 + cnt - 1;
-  if (__ldg(pos + r0 + 1) <= last) {  // chunk crosses a row boundary
-    const int p = (int)p0 + min(lane, cnt - 1);
-    r = row_of_entry(pos, r0, m, p);
+// Row of entry p, searching forward from row r (pos[r] <= p): a few steps of linear walk (the
+// common case: the next chunk starts in the same or the next row), then a bounded binary search.
+__device__ __forceinline__ int advance_row(const int* __restrict__ pos, int m, int r, int p) {
+#pragma unroll 1
+  for (int t = 0; t < 4; t++) {
+    if (__ldg(pos + r + 1) > p) return r;
+    r++;
   }
-  return r;
+  return row_of_entry(pos, r, m, p);
 }
+
+constexpr int kChunksPerWarp = 8;  // a warp owns 8 consecutive 32-entry chunks: one row search
 
 template <int G, int VEC>
 __global__ void __launch_bounds__(kSddmmWarps * 32)
 sddmm_kernel(SddmmArgs a) {
   constexpr int NG = 32 / G;  // entries in flight per step
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long chunk = (long long)blockIdx.x * kSddmmWarps + warp;
-  const long long p0 = chunk * 32;
+  const long long span = (long long)blockIdx.x * kSddmmWarps + warp;
+  long long p0 = span * (32 * kChunksPerWarp);
   if (p0 >= a.nnz) return;
-  const int cnt = (int)min((long long)32, a.nnz - p0);
+  const long long p_end = min(a.nnz, p0 + 32 * kChunksPerWarp);
   const long long bz = blockIdx.y;
   const float* Q = a.Q + bz * a.stride_q;
   const float* K = a.K + bz * a.stride_k;
-
-  int my_j = 0, my_i = 0;
-  float my_s = 1.f;
-  if (lane < cnt) {
-    my_j = ld_stream(a.crd + p0 + lane);
-    if (a.mask_val) my_s = ld_stream(a.mask_val + p0 + lane);
-    if (a.row) my_i = ld_stream(a.row + p0 + lane);
-  }
-  if (a.pos) my_i = chunk_rows(a.pos, a.m, p0, cnt, lane);
-  if (bz == 0 && lane < cnt) {
-    if (a.out_row) a.out_row[p0 + lane] = my_i;
-    if (a.out_col) a.out_col[p0 + lane] = my_j;
-  }
+  float* out = a.out_val + bz * a.stride_out;
 
   const int g = lane / G, l = lane % G;
   bool col_ok[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; v++) col_ok[v] = (l + v * G) * 4 < a.d;
-
   float4 q[VEC];
   int q_row = -1;
-  float my_res = 0.f;
-  constexpr int U = (G >= 4) ? 4 : G;  // steps unrolled together: U K-row loads in flight
+  int r0 = a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0;
+
 #pragma unroll 1
-  for (int s0 = 0; s0 < G; s0 += U) {
-    int jj[U], ii[U];
-    float4 kv[U][VEC];
-    bool ok[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      const int idx = (s0 + u) * NG + g;
-      jj[u] = __shfl_sync(FULL, my_j, idx);
-      ii[u] = __shfl_sync(FULL, my_i, idx);
-      ok[u] = idx < cnt;
+  for (; p0 < p_end; p0 += 32) {
+    const int cnt = (int)min((long long)32, p_end - p0);
+    int my_j = 0, my_i = 0;
+    float my_s = 1.f;
+    if (lane < cnt) {
+      my_j = ld_stream(a.crd + p0 + lane);
+      if (a.mask_val) my_s = ld_stream(a.mask_val + p0 + lane);
+      if (a.row) my_i = ld_stream(a.row + p0 + lane);
     }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      const float* krow = K + (long long)jj[u] * a.ldk;
-#pragma unroll
-      for (int v = 0; v < VEC; v++)
-        kv[u][v] = (ok[u] && col_ok[v]) ? ldg4(krow + (l + v * G) * 4)
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a.pos) {
+      r0 = advance_row(a.pos, a.m, r0, (int)p0);  // warp-uniform
+      my_i = r0;
+      if (__ldg(a.pos + r0 + 1) <= (int)p0 + cnt - 1)  // the chunk crosses a row boundary
+        my_i = row_of_entry(a.pos, r0, a.m, (int)p0 + min(lane, cnt - 1));
     }
+    if (bz == 0 && lane < cnt) {
+      if (a.out_row) a.out_row[p0 + lane] = my_i;
+      if (a.out_col) a.out_col[p0 + lane] = my_j;
+    }
+
+    float my_res = 0.f;
+    constexpr int U = (G >= 2) ? 2 : 1;  // steps unrolled together: U*VEC K loads in flight
 #pragma unroll
-    for (int u = 0; u < U; u++) {
-      if (ok[u] && ii[u] != q_row) {
-        q_row = ii[u];
-        const float* qrow = Q + (long long)q_row * a.ldq;
+    for (int s0 = 0; s0 < G; s0 += U) {
+      int jj[U], ii[U];
+      float4 kv[U][VEC];
+      bool ok[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int idx = (s0 + u) * NG + g;
+        jj[u] = __shfl_sync(FULL, my_j, idx);
+        ii[u] = __shfl_sync(FULL, my_i, idx);
+        ok[u] = idx < cnt;
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const float* krow = K + (long long)jj[u] * a.ldk + l * 4;
 #pragma unroll
         for (int v = 0; v < VEC; v++)
-          q[v] = col_ok[v] ? ldg4(qrow + (l + v * G) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          kv[u][v] = (ok[u] && col_ok[v]) ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      float part = 0.f;
-      if (ok[u]) {
 #pragma unroll
-        for (int v = 0; v < VEC; v++) part = dot4(q[v], kv[u][v], part);
+      for (int u = 0; u < U; u++) {
+        if (ok[u] && ii[u] != q_row) {
+          q_row = ii[u];
+          const float* qrow = Q + (long long)q_row * a.ldq + l * 4;
+#pragma unroll
+          for (int v = 0; v < VEC; v++)
+            q[v] = col_ok[v] ? ldg4(qrow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float part = 0.f;
+        if (ok[u]) {
+#pragma unroll
+          for (int v = 0; v < VEC; v++) part = dot4(q[v], kv[u][v], part);
+        }
+        part = group_sum<G>(part);
+        if (l == s0 + u) my_res = part;  // lane (g, l) keeps entry l*NG + g
       }
-      part = group_sum<G>(part);
-      if (l == s0 + u) my_res = part;  // lane (g, l) keeps entry l*NG + g
     }
+    const int my_idx = l * NG + g;
+    const float s = __shfl_sync(FULL, my_s, my_idx);
+    if (my_idx < cnt) out[p0 + my_idx] = s * my_res;
   }
-  const int my_idx = l * NG + g;
-  const float s = __shfl_sync(FULL, my_s, my_idx);
-  if (my_idx < cnt) a.out_val[bz * a.stride_out + p0 + my_idx] = s * my_res;
 }
 
 // Any d / any alignment: one lane per entry, scalar loop over d.
@@ -146,8 +155,8 @@ __global__ void sddmm_generic_kernel(SddmmArgs a) {
 
 template <int G, int VEC>
 static int launch_sddmm(const SddmmArgs& a, int64_t batch, cudaStream_t st) {
-  const long long chunks = ceil_div(a.nnz, 32);
-  dim3 grid((unsigned)ceil_div(chunks, kSddmmWarps), (unsigned)batch);
+  const long long spans = ceil_div(a.nnz, 32 * kChunksPerWarp);
+  dim3 grid((unsigned)ceil_div(spans, kSddmmWarps), (unsigned)batch);
   sddmm_kernel<G, VEC><<<grid, kSddmmWarps * 32, 0, st>>>(a);
   SB_LAUNCH_CHECK("sddmm_kernel");
   return SB_OK;
@@ -164,11 +173,12 @@ static int sddmm_dispatch(SddmmArgs a, int64_t batch, cudaStream_t st) {
     SB_LAUNCH_CHECK("sddmm_generic_kernel");
     return SB_OK;
   }
+  // G lanes share one dot product, each holding VEC float4 of the Q row (G*VEC*4 >= d)
   if (a.d <= 16) return launch_sddmm<4, 1>(a, batch, st);
-  if (a.d <= 32) return launch_sddmm<8, 1>(a, batch, st);
-  if (a.d <= 64) return launch_sddmm<8, 2>(a, batch, st);
-  if (a.d <= 128) return launch_sddmm<16, 2>(a, batch, st);
-  if (a.d <= 256) return launch_sddmm<32, 2>(a, batch, st);
+  if (a.d <= 32) return launch_sddmm<4, 2>(a, batch, st);
+  if (a.d <= 64) return launch_sddmm<4, 4>(a, batch, st);
+  if (a.d <= 128) return launch_sddmm<8, 4>(a, batch, st);
+  if (a.d <= 256) return launch_sddmm<16, 4>(a, batch, st);
   return launch_sddmm<32, 4>(a, batch, st);
 }
 
