@@ -125,6 +125,23 @@ SB_API int sb_spmv_csr_typed(int dtype, int64_t m, int64_t n, int64_t nnz, const
                              const int32_t* crd, const void* val, const void* x, void* y,
                              void* stream);
 
+/* SpMV that allocates nothing and asks the caller for no workspace.  (No counterpart in the
+ * reference: its kernels malloc freely on the host.)  For callers that cannot call cudaMalloc —
+ * a plugin living inside another runtime's device-memory arena, or a service that must not touch
+ * the allocator after start-up.  Same result as sb_spmv_csr_f32; the row plan and the segment
+ * scratch live in an array of SB_STATIC_SCRATCH_BYTES that is part of the library image, so each
+ * GPU that loads the library holds that much memory until the process exits.
+ *   - nnz above SB_STATIC_SPMV_MAX_NNZ is rejected with SB_ERR_UNSUPPORTED.
+ *   - The first call on a device resolves the array's device address; make that call outside of
+ *     any stream capture.
+ *   - All calls share the array: calls that overlap on one GPU (other streams, other threads)
+ *     race.  Serialise them, or use sb_spmv_csr_f32 with buffers of your own. */
+#define SB_STATIC_SPMV_MAX_NNZ (1LL << 26)
+#define SB_STATIC_SCRATCH_BYTES (2 << 20)
+SB_API int sb_spmv_csr_f32_static(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                                  const int32_t* crd, const float* val, const float* x, float* y,
+                                  void* stream);
+
 /* --------------------------------------------------------------------------------------------
  * SDDMM: out_val[p] = mask_val[p] * dot(Q[i_p, 0:d], K[j_p, 0:d]) for every stored (i_p, j_p) of
  * the mask, in the mask's entry order.  mask_val may be NULL (all ones).  K is (n, d) row-major,

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libscorch_b200.so")
 SB_OK = 0
 SB_F32, SB_F64, SB_I32, SB_I64 = 0, 1, 2, 3
 HEAVY_ROW_NNZ = 1024
+STATIC_SPMV_MAX_NNZ = 1 << 26
 
 _i64, _int, _ptr, _sz, _f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
 
@@ -35,6 +36,7 @@ SIGNATURES = {
     "sb_spmv_csr_f32": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                _sz, _ptr]),
     "sb_spmv_csr_typed": (_int, [_int, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "sb_spmv_csr_f32_static": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "sb_sddmm_csr_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64,
                                 _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "sb_sddmm_coo_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64,
