@@ -70,20 +70,31 @@ def plan_for(pos: torch.Tensor, nnz: int) -> CsrPlan:
     return plan
 
 
+def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
+    """2-D operand whose rows are contiguous; the row pitch (leading dimension) may exceed the width."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
+        return t
+    return t.contiguous()
+
+
 def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[CsrPlan] = None,
              out: Optional[torch.Tensor] = None, n: Optional[int] = None) -> torch.Tensor:
     """C = act(bias + A @ B) for CSR A.  ``B`` is (n, k) or (batch, n, k); ``val`` is (nnz,) —
-    shared by all batch items — or (batch, nnz).  Returns (m, k) or (batch, m, k)."""
+    shared by all batch items — or (batch, nnz).  Returns (m, k) or (batch, m, k).
+    2-D ``B`` / ``out`` may be column slices of wider row-major buffers (row pitch > k)."""
     pos = _dev(pos, torch.int32, "pos")
     crd = _dev(crd, torch.int32, "crd")
     m, nnz = pos.numel() - 1, crd.numel()
     if val.dtype != torch.float32:
         return _spmm_typed(pos, crd, val, B, n)
     val = _dev(val, torch.float32, "val")
-    B = _dev(B, torch.float32, "B")
+    if not (isinstance(B, torch.Tensor) and B.is_cuda and B.dtype == torch.float32):
+        B = _dev(B, torch.float32, "B")
     batched = B.dim() == 3
+    B = B.contiguous() if batched else _row_major_2d(B, "B")
     batch = B.shape[0] if batched else 1
     nb, k = B.shape[-2], B.shape[-1]
+    ldb = k if batched else B.stride(0)
     if val.dim() == 2:
         if val.shape[0] != batch or val.shape[1] != nnz:
             raise ValueError("val must be (nnz,) or (batch, nnz)")
@@ -99,10 +110,18 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
     shape = (batch, m, k) if batched else (m, k)
     if out is None:
         out = torch.empty(shape, dtype=torch.float32, device=B.device)
+        ldc = k
     else:
-        out = _dev(out, torch.float32, "out")
-        if tuple(out.shape) != shape:
-            raise ValueError(f"out must have shape {shape}")
+        if not (out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == shape):
+            raise ValueError(f"out must be a float32 CUDA tensor of shape {shape}")
+        if batched:
+            if not out.is_contiguous():
+                raise ValueError("batched out must be contiguous")
+            ldc = k
+        else:
+            if out.stride(1) != 1 or out.stride(0) < k:
+                raise ValueError("out rows must be contiguous")
+            ldc = out.stride(0)
     if plan is None:
         plan = plan_for(pos, nnz)
     L = _lib.lib()
@@ -110,8 +129,8 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
     scratch = plan.scratch(sbytes) if sbytes else None
     with torch.cuda.device(B.device):
         check(L.sb_spmm_csr_f32(m, nb if n is None else n, k, nnz, pos.data_ptr(), crd.data_ptr(),
-                                val.data_ptr(), B.data_ptr(), k, _ptr(bias), int(bool(relu)),
-                                out.data_ptr(), k, batch, stride_val, nb * k, m * k,
+                                val.data_ptr(), B.data_ptr(), ldb, _ptr(bias), int(bool(relu)),
+                                out.data_ptr(), ldc, batch, stride_val, nb * k, m * k,
                                 plan.buf.data_ptr(), plan.segments, _ptr(scratch), sbytes,
                                 _stream()))
     return out
