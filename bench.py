@@ -136,7 +136,8 @@ class SparseAttention:
         self.plan = K.CsrPlan(self.pos, self.nnz)
         self.scores = torch.empty((self.units, self.nnz), dtype=torch.float32, device="cuda")
         self.out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, device="cuda")
-        self.stage = [torch.empty_like(t, device="cuda") for t in self.host]
+        from scorch_b200 import pipelines as P
+        self.host_api = P.HostSparseAttention(self.pos, self.crd, self.mval, self.units, self.seq, self.d)
 
     @property
     def flops_per_step(self):  # SDDMM + SpMM, 2*nnz*d each (the reference tools' convention)
@@ -162,8 +163,7 @@ class SparseAttention:
         if ev is not None:
             ev[0].record()
         # same calls as pipelines.sparse_attention, with preallocated outputs
-        s = self.scores
-        self._sddmm(Q, Km, s)
+        s = K.sddmm_csr(self.pos, self.crd, self.mval, Q, Km, out=self.scores)
         if ev is not None:
             ev[1].record()
         K.csr_row_softmax(self.pos, s, out=s)
@@ -173,15 +173,6 @@ class SparseAttention:
         if ev is not None:
             ev[3].record()
 
-    def _sddmm(self, Q, Km, out):
-        from scorch_b200 import _lib
-        L = _lib.lib()
-        _lib.check(L.sb_sddmm_csr_f32(self.seq, self.seq, self.d, self.nnz, self.pos.data_ptr(),
-                                      self.crd.data_ptr(), self.mval.data_ptr(), Q.data_ptr(), self.d,
-                                      Km.data_ptr(), self.d, out.data_ptr(), None, None, self.units,
-                                      self.seq * self.d, self.seq * self.d, self.nnz,
-                                      torch.cuda.current_stream().cuda_stream))
-
     kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
     launches_per_step = 3
 
@@ -189,11 +180,8 @@ class SparseAttention:
         self._run(self.Q, self.Km, self.V, ev)
 
     def e2e_step(self):
-        for dst, src in zip(self.stage, self.host):
-            dst.copy_(src, non_blocking=True)
-        self._run(*self.stage)
-        self.host_out.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        # the public host-tensor call: pinned Q, K, V in, pinned O out, copies inside
+        self.host_api(*self.host, out_host=self.host_out)
 
     @property
     def h2d_bytes(self):
@@ -527,7 +515,7 @@ def make_workload(name: str, world: int = 1):
 
 
 # ---- reference arm --------------------------------------------------------------------------------
-def run_reference(args, rank: int):
+def run_reference(args, rank: int, emit):
     if rank != 0:
         return
     wl = make_workload(args.workload)
@@ -562,7 +550,7 @@ def run_reference(args, rank: int):
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(line)
 
 
 # ---- main -------------------------------------------------------------------------------------------
@@ -581,9 +569,17 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Libraries print banners to stdout (NCCL's version line): keep stdout for the one JSON line.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line: dict):
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, emit)
         return
 
     if not torch.cuda.is_available():
@@ -686,7 +682,7 @@ def main():
                 "dtype": "f32", "data": "synthetic", "config": wl.config(), "e2e": e2e,
                 "gpu_launches": K * wl.launches_per_step, "roofline": roofline, "cpu_baseline": cpu_baseline,
                 "clocks": clocks}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

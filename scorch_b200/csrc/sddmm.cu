@@ -48,7 +48,7 @@ __device__ __forceinline__ int advance_row(const int* __restrict__ pos, int m, i
 constexpr int kChunksPerWarp = 8;  // a warp owns 8 consecutive 32-entry chunks: one row search
 
 template <int G, int VEC>
-__global__ void __launch_bounds__(kSddmmWarps * 32)
+__global__ void __launch_bounds__(kSddmmWarps * 32, 3)
 sddmm_kernel(SddmmArgs a) {
   constexpr int NG = 32 / G;  // entries in flight per step
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,15 +69,25 @@ sddmm_kernel(SddmmArgs a) {
   int q_row = -1;
   int r0 = a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0;
 
+  // software pipeline: the next chunk's entries are in flight while this chunk's K rows are
+  // gathered
+  int next_j = 0, next_i = 0;
+  float next_s = 1.f;
+  if (p0 + lane < p_end) {
+    next_j = ld_stream(a.crd + p0 + lane);
+    if (a.mask_val) next_s = ld_stream(a.mask_val + p0 + lane);
+    if (a.row) next_i = ld_stream(a.row + p0 + lane);
+  }
 #pragma unroll 1
   for (; p0 < p_end; p0 += 32) {
     const int cnt = (int)min((long long)32, p_end - p0);
-    int my_j = 0, my_i = 0;
-    float my_s = 1.f;
-    if (lane < cnt) {
-      my_j = ld_stream(a.crd + p0 + lane);
-      if (a.mask_val) my_s = ld_stream(a.mask_val + p0 + lane);
-      if (a.row) my_i = ld_stream(a.row + p0 + lane);
+    const int my_j = next_j;
+    int my_i = next_i;
+    const float my_s = next_s;
+    if (p0 + 32 + lane < p_end) {
+      next_j = ld_stream(a.crd + p0 + 32 + lane);
+      if (a.mask_val) next_s = ld_stream(a.mask_val + p0 + 32 + lane);
+      if (a.row) next_i = ld_stream(a.row + p0 + 32 + lane);
     }
     if (a.pos) {
       r0 = advance_row(a.pos, a.m, r0, (int)p0);  // warp-uniform

@@ -9,8 +9,8 @@
 //   bin 4  U  > 8192    dense bitmap (+ dense accumulator) of n columns in the workspace, a
 //                       bounded pool of persistent CTAs walks these rows
 // Hash bins: open addressing with atomicCAS on the column key (+ atomicAdd on the value), load
-// factor <= 0.5 by construction.  The numeric phase sorts each row's table in shared memory
-// (bitonic, empty slots = INT_MAX sink to the end) so columns come out ascending like the
+// factor <= 0.5 by construction.  The numeric phase compacts each row's table in place and sorts
+// the occupied part in shared memory (bitonic) so columns come out ascending like the
 // reference's per-row sort; the dense bin emits columns in bitmap order, which is already
 // ascending.  The structure is the symbolic union: a slot whose value cancels to 0 is kept.
 // Row pointers come from a three-kernel exclusive scan in int64, stored as int32 with an
@@ -135,11 +135,12 @@ __device__ __forceinline__ int hash_insert(int* keys, T* vals, int c, T v) {
   }
 }
 
-template <typename T, int S, int NT, bool WARP_SCOPE>
-__device__ __forceinline__ void bitonic_sort(int* keys, T* vals, int tid) {
-  for (int k = 2; k <= S; k <<= 1) {
+// Bitonic sort of the first P slots (P a power of two <= S) by key, values carried along.
+template <typename T, int NT, bool WARP_SCOPE>
+__device__ __forceinline__ void bitonic_sort(int* keys, T* vals, int P, int tid) {
+  for (int k = 2; k <= P; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = tid; t < S / 2; t += NT) {
+      for (int t = tid; t < P / 2; t += NT) {
         const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
         const int x = i | j;
         const bool up = (i & k) == 0;
@@ -152,6 +153,52 @@ __device__ __forceinline__ void bitonic_sort(int* keys, T* vals, int tid) {
       if (WARP_SCOPE) __syncwarp(); else __syncthreads();
     }
   }
+}
+
+// Moves the occupied slots of a hash table to the front, in place, NT slots per round: a round
+// reads its slots into registers, scans the occupancy, and writes them at the running offset,
+// which never runs ahead of the slots already read.  Then pads up to the next power of two with
+// empty keys and returns that size (what the sort has to cover).  One warp (WARP_SCOPE) or one
+// CTA of NT threads; `s_scan` is NT/32 + 1 ints of shared memory (unused for a warp).
+template <typename T, int S, int NT, bool WARP_SCOPE>
+__device__ __forceinline__ int compact_table(int* keys, T* vals, int tid, int* s_scan) {
+  const int lane = tid & 31, warp = tid >> 5;
+  int run = 0;
+  for (int r0 = 0; r0 < S; r0 += NT) {
+    const int key = keys[r0 + tid];
+    const T val = vals[r0 + tid];
+    const bool occ = key != kEmpty;
+    const unsigned ball = __ballot_sync(FULL, occ);
+    int off = __popc(ball & ((1u << lane) - 1));
+    int total = __popc(ball);
+    if (!WARP_SCOPE) {
+      if (lane == 0) s_scan[warp] = total;
+      __syncthreads();  // also: every slot of this round has been read
+      int before = 0;
+      total = 0;
+#pragma unroll
+      for (int w = 0; w < NT / 32; w++) {
+        const int c = s_scan[w];
+        if (w < warp) before += c;
+        total += c;
+      }
+      off += before;
+      __syncthreads();  // s_scan is rewritten next round
+    } else {
+      __syncwarp();
+    }
+    if (occ) {
+      keys[run + off] = key;
+      vals[run + off] = val;
+    }
+    run += total;
+    if (WARP_SCOPE) __syncwarp(); else __syncthreads();
+  }
+  int P = 1;
+  while (P < run) P <<= 1;
+  for (int t = run + tid; t < P; t += NT) keys[t] = kEmpty;
+  if (WARP_SCOPE) __syncwarp(); else __syncthreads();
+  return P;
 }
 
 struct CsrIn {
@@ -201,7 +248,8 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
     for (int o = 16; o > 0; o >>= 1) fresh += __shfl_xor_sync(FULL, fresh, o);
     if (lane == 0) row_cnt[i] = fresh;
   } else {
-    bitonic_sort<T, S, 32, true>(keys, vals, lane);
+    const int P = compact_table<T, S, 32, true>(keys, vals, lane, nullptr);
+    bitonic_sort<T, 32, true>(keys, vals, P, lane);
     const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
     for (int t = lane; t < cnt; t += 32) {
       Ccrd[base + t] = keys[t];
@@ -219,6 +267,7 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
   T* vals = reinterpret_cast<T*>(smem_raw);                       // S values (numeric only)
   int* keys = reinterpret_cast<int*>(smem_raw + (NUMERIC ? sizeof(T) * S : 0));
   __shared__ int s_fresh;
+  __shared__ int s_scan[NT / 32 + 1];
   const int r = blockIdx.x;
   if (r >= nrows) return;
   const int i = __ldg(rows + r);
@@ -253,7 +302,8 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
     if (tid == 0) row_cnt[i] = s_fresh;
   } else {
     __syncthreads();
-    bitonic_sort<T, S, NT, false>(keys, vals, tid);
+    const int P = compact_table<T, S, NT, false>(keys, vals, tid, s_scan);
+    bitonic_sort<T, NT, false>(keys, vals, P, tid);
     const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
     for (int t = tid; t < cnt; t += NT) {
       Ccrd[base + t] = keys[t];

@@ -42,13 +42,21 @@ __device__ __forceinline__ void accumulate_range(float4 (&acc)[VEC], const int* 
                                                  int b, int e, int lane, bool col_ok[VEC]) {
   constexpr int G = 32 / L;
   const int g = lane / L;
+  // software pipeline: the next chunk's indices/values are in flight while this chunk's rows of
+  // the dense operand are gathered
+  int next_j = 0;
+  float next_a = 0.f;
+  if (b + lane < e) {
+    next_j = ld_stream(crd + b + lane);
+    next_a = ld_stream(val + b + lane);
+  }
   for (int p0 = b; p0 < e; p0 += 32) {
     const int cnt = min(32, e - p0);
-    int my_j = 0;
-    float my_a = 0.f;
-    if (lane < cnt) {
-      my_j = ld_stream(crd + p0 + lane);
-      my_a = ld_stream(val + p0 + lane);
+    const int my_j = next_j;
+    const float my_a = next_a;
+    if (p0 + 32 + lane < e) {
+      next_j = ld_stream(crd + p0 + 32 + lane);
+      next_a = ld_stream(val + p0 + 32 + lane);
     }
     if (cnt == 32) {
       constexpr int STEPS = 32 / G;

@@ -190,7 +190,8 @@ def _qk(Q, K):
     return Q, K, batch
 
 
-def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False):
+def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
+              out: Optional[torch.Tensor] = None):
     """out[p] = mask_val[p] * <Q[i_p], K[j_p]> over the entries of a CSR mask, entry order kept.
     Returns values (nnz,) or (batch, nnz); with ``want_coords`` also fresh int32 (row, col)."""
     pos = _dev(pos, torch.int32, "pos")
@@ -199,7 +200,12 @@ def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False):
     m, nnz, d = pos.numel() - 1, crd.numel(), Q.shape[-1]
     if mask_val is not None:
         mask_val = _dev(mask_val, torch.float32, "mask_val")
-    out = torch.empty((batch, nnz) if Q.dim() == 3 else (nnz,), dtype=torch.float32, device=Q.device)
+    shape = (batch, nnz) if Q.dim() == 3 else (nnz,)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=Q.device)
+    elif not (out.is_cuda and out.dtype == torch.float32 and out.is_contiguous()
+              and tuple(out.shape) == shape):
+        raise ValueError(f"out must be a contiguous float32 CUDA tensor of shape {shape}")
     row = col = None
     if want_coords:
         row = torch.empty(nnz, dtype=torch.int32, device=Q.device)

@@ -36,3 +36,52 @@ def gcn_forward(pos, crd, val, X, W1, W2, plan: Optional[K.CsrPlan] = None) -> t
     h = K.spmm_csr(pos, crd, val, xw, relu=True, plan=plan)
     hw = torch.matmul(h, W2)
     return K.spmm_csr(pos, crd, val, hw, plan=plan)
+
+
+class HostSparseAttention:
+    """``sparse_attention`` for operands that live in (pinned) host memory, as the reference's
+    callers hold them: the (batch*heads) units are cut into chunks and pipelined over three
+    streams — host->device copy of chunk c+1, kernels of chunk c and device->host copy of chunk
+    c-1 overlap, so a step costs about the PCIe time of its inputs instead of copy + compute."""
+
+    def __init__(self, pos, crd, mask_val, units: int, seq: int, d: int, chunks: int = 4,
+                 scale: float = 1.0):
+        dev = pos.device
+        self.pos, self.crd, self.mask_val, self.scale = pos, crd, mask_val, scale
+        self.units, self.seq, self.d = units, seq, d
+        self.plan = K.plan_for(pos, crd.numel())
+        self.bounds = [units * c // chunks for c in range(chunks + 1)]
+        self.dev = [torch.empty((units, seq, d), dtype=torch.float32, device=dev) for _ in range(3)]
+        self.scores = torch.empty((units, crd.numel()), dtype=torch.float32, device=dev)
+        self.out = torch.empty((units, seq, d), dtype=torch.float32, device=dev)
+        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def __call__(self, Qh: torch.Tensor, Kh: torch.Tensor, Vh: torch.Tensor,
+                 out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out_host is None:
+            out_host = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, pin_memory=True)
+        main = torch.cuda.current_stream()
+        self.s_in.wait_stream(main)      # earlier work on these buffers is done
+        self.s_out.wait_stream(main)
+        for c in range(len(self.bounds) - 1):
+            u0, u1 = self.bounds[c], self.bounds[c + 1]
+            if u0 == u1:
+                continue
+            with torch.cuda.stream(self.s_in):
+                for dst, src in zip(self.dev, (Qh, Kh, Vh)):
+                    dst[u0:u1].copy_(src[u0:u1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(self.s_in)
+            main.wait_event(arrived)
+            s = K.sddmm_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1], self.dev[1][u0:u1],
+                            out=self.scores[u0:u1])
+            K.csr_row_softmax(self.pos, s, scale=self.scale, out=s)
+            K.spmm_csr(self.pos, self.crd, s, self.dev[2][u0:u1], plan=self.plan, out=self.out[u0:u1])
+            computed = torch.cuda.Event()
+            computed.record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(computed)
+                out_host[u0:u1].copy_(self.out[u0:u1], non_blocking=True)
+        main.wait_stream(self.s_out)
+        main.synchronize()
+        return out_host

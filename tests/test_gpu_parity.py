@@ -278,6 +278,19 @@ def test_c2_sparse_attention_reduced_and_batched(oracle):
         assert_close(oracle, O[u], o64, f"attention output unit {u}")
 
 
+def test_host_sparse_attention_pipeline_matches_device_path():
+    """Pinned host operands, chunked copy/compute overlap: same numbers as the resident path."""
+    from scorch_b200 import pipelines as P, workloads as W
+    mask = W.attention_mask(512, window=16, density=0.02, seed=3)
+    Q, Km, V = (t.pin_memory() for t in W.attention_qkv(1, 7, 512, 64, seed=4))
+    pos, crd, mv = dev(mask.pos), dev(mask.crd), dev(mask.val)
+    want = P.sparse_attention(pos, crd, mv, Q.cuda(), Km.cuda(), V.cuda(), scale=0.125).cpu()
+    host = P.HostSparseAttention(pos, crd, mv, units=7, seq=512, d=64, chunks=3, scale=0.125)
+    for _ in range(2):  # buffers and streams are reused from call to call
+        got = host(Q, Km, V)
+        assert not got.is_cuda and torch.equal(got, want)
+
+
 def test_c3_sae_decode_reduced(oracle):
     from scorch_b200 import kernels as K, workloads as W
     A = W.sae_activations(512, 4096, 32, seed=0)
