@@ -5,9 +5,10 @@
 // span, so the split is balanced by nnz whatever the row lengths are.  Per 32-entry chunk the
 // warp reads the column ids / mask values with one coalesced load and finds each entry's row
 // (one binary search per span, a short forward walk per chunk, a per-lane refinement only when
-// a chunk crosses rows); then G lanes compute one dot product with 128-bit loads of the K row
-// and a shuffle tree, and the Q row stays in registers while consecutive entries share it.
-// Results are written back one coalesced line per chunk.
+// a chunk crosses rows); then G lanes share each dot product: 128-bit loads of whole K-row lines,
+// the Q row kept in registers while consecutive entries share it, and a transpose-reduce that
+// costs about one shuffle per entry and leaves entry t of the chunk on lane t, so results are
+// written back as one coalesced line per chunk.
 #include <math.h>
 
 #include "common.cuh"
@@ -47,27 +48,62 @@ __device__ __forceinline__ int advance_row(const int* __restrict__ pos, int m, i
 
 constexpr int kChunksPerWarp = 8;  // a warp owns 8 consecutive 32-entry chunks: one row search
 
-template <int G, int VEC>
-__global__ void __launch_bounds__(kSddmmWarps * 32, 3)
+// Sums G per-lane partial values for G entries across the G lanes of a group with G-1 shuffles
+// (a butterfly that halves the number of live values per lane at every step).  On return lane l
+// of the group holds, in v[0], the complete sum for entry l.
+template <int G>
+__device__ __forceinline__ void transpose_reduce(float (&v)[G], int lane) {
+#pragma unroll
+  for (int o = G / 2; o >= 1; o >>= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; i++) {
+      const float send = upper ? v[i] : v[i + o];
+      const float keep = upper ? v[i + o] : v[i];
+      v[i] = keep + __shfl_xor_sync(FULL, send, o);
+    }
+  }
+}
+
+// G lanes per dot product, VEC float4 of the Q/K row per lane (G*VEC*4 >= d; EXACT: == d, no
+// column predicates).  A 32-entry chunk is handled as 32/G groups of G consecutive entries: a
+// group gathers its G K rows (each row read by G adjacent lanes: whole 128-byte lines), forms G
+// partial dots per lane and transpose-reduces them, after which lane t of the warp owns entry t
+// of the chunk.  Full chunks that lie inside one mask row take a path without per-entry row
+// bookkeeping or predicates.
+template <int G, int VEC, bool EXACT>
+__global__ void __launch_bounds__(kSddmmWarps * 32, (VEC >= 4 || G >= 32) ? 2 : 3)
 sddmm_kernel(SddmmArgs a) {
-  constexpr int NG = 32 / G;  // entries in flight per step
+  // K rows gathered together: about 8 128-bit loads in flight per lane
+  constexpr int HALF = (8 / VEC < G) ? (8 / VEC) : G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long span = (long long)blockIdx.x * kSddmmWarps + warp;
   long long p0 = span * (32 * kChunksPerWarp);
   if (p0 >= a.nnz) return;
   const long long p_end = min(a.nnz, p0 + 32 * kChunksPerWarp);
   const long long bz = blockIdx.y;
-  const float* Q = a.Q + bz * a.stride_q;
-  const float* K = a.K + bz * a.stride_k;
+  const int g0 = (lane / G) * G, l = lane % G;  // first lane of my group, my slice of the row
+  const float* Q = a.Q + bz * a.stride_q + l * 4;
+  const float* K = a.K + bz * a.stride_k + l * 4;
   float* out = a.out_val + bz * a.stride_out;
+  const unsigned ldq = (unsigned)a.ldq, ldk = (unsigned)a.ldk;  // row pitches fit 32 bits
 
-  const int g = lane / G, l = lane % G;
   bool col_ok[VEC];
 #pragma unroll
-  for (int v = 0; v < VEC; v++) col_ok[v] = (l + v * G) * 4 < a.d;
+  for (int v = 0; v < VEC; v++) col_ok[v] = EXACT || (l + v * G) * 4 < a.d;
   float4 q[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; v++) q[v] = make_float4(0.f, 0.f, 0.f, 0.f);
   int q_row = -1;
   int r0 = a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0;
+
+  auto load_q = [&](int row) {
+    q_row = row;
+    const float* qrow = Q + (size_t)((unsigned long long)(unsigned)row * ldq);
+#pragma unroll
+    for (int v = 0; v < VEC; v++)
+      if (col_ok[v]) q[v] = ldg4(qrow + v * G * 4);
+  };
 
   // software pipeline: the next chunk's entries are in flight while this chunk's K rows are
   // gathered
@@ -89,59 +125,61 @@ sddmm_kernel(SddmmArgs a) {
       if (a.mask_val) next_s = ld_stream(a.mask_val + p0 + 32 + lane);
       if (a.row) next_i = ld_stream(a.row + p0 + 32 + lane);
     }
+    bool one_row = false;  // warp-uniform: every entry of the chunk lies in row r0
     if (a.pos) {
-      r0 = advance_row(a.pos, a.m, r0, (int)p0);  // warp-uniform
+      r0 = advance_row(a.pos, a.m, r0, (int)p0);
       my_i = r0;
-      if (__ldg(a.pos + r0 + 1) <= (int)p0 + cnt - 1)  // the chunk crosses a row boundary
-        my_i = row_of_entry(a.pos, r0, a.m, (int)p0 + min(lane, cnt - 1));
+      one_row = __ldg(a.pos + r0 + 1) > (int)p0 + cnt - 1;
+      if (!one_row) my_i = row_of_entry(a.pos, r0, a.m, (int)p0 + min(lane, cnt - 1));
     }
     if (bz == 0 && lane < cnt) {
       if (a.out_row) a.out_row[p0 + lane] = my_i;
       if (a.out_col) a.out_col[p0 + lane] = my_j;
     }
 
-    float my_res = 0.f;
-    constexpr int U = (G >= 2) ? 2 : 1;  // steps unrolled together: U*VEC K loads in flight
+    float part[G];
+    if (one_row && cnt == 32) {
+      if (r0 != q_row) load_q(r0);
 #pragma unroll
-    for (int s0 = 0; s0 < G; s0 += U) {
-      int jj[U], ii[U];
-      float4 kv[U][VEC];
-      bool ok[U];
+      for (int t0 = 0; t0 < G; t0 += HALF) {
+        float4 kv[HALF][VEC];
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        const int idx = (s0 + u) * NG + g;
-        jj[u] = __shfl_sync(FULL, my_j, idx);
-        ii[u] = __shfl_sync(FULL, my_i, idx);
-        ok[u] = idx < cnt;
-      }
-#pragma unroll
-      for (int u = 0; u < U; u++) {
-        const float* krow = K + (long long)jj[u] * a.ldk + l * 4;
-#pragma unroll
-        for (int v = 0; v < VEC; v++)
-          kv[u][v] = (ok[u] && col_ok[v]) ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < U; u++) {
-        if (ok[u] && ii[u] != q_row) {
-          q_row = ii[u];
-          const float* qrow = Q + (long long)q_row * a.ldq + l * 4;
+        for (int u = 0; u < HALF; u++) {
+          const unsigned j = (unsigned)__shfl_sync(FULL, my_j, g0 + t0 + u);
+          const float* krow = K + (size_t)((unsigned long long)j * ldk);
 #pragma unroll
           for (int v = 0; v < VEC; v++)
-            q[v] = col_ok[v] ? ldg4(qrow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            kv[u][v] = col_ok[v] ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        float part = 0.f;
-        if (ok[u]) {
 #pragma unroll
-          for (int v = 0; v < VEC; v++) part = dot4(q[v], kv[u][v], part);
+        for (int u = 0; u < HALF; u++) {
+          float acc = 0.f;
+#pragma unroll
+          for (int v = 0; v < VEC; v++) acc = dot4(q[v], kv[u][v], acc);
+          part[t0 + u] = acc;
         }
-        part = group_sum<G>(part);
-        if (l == s0 + u) my_res = part;  // lane (g, l) keeps entry l*NG + g
+      }
+    } else {
+#pragma unroll 1
+      for (int t = 0; t < G; t++) {
+        const int idx = g0 + t;
+        const unsigned j = (unsigned)__shfl_sync(FULL, my_j, idx);
+        const int i = __shfl_sync(FULL, my_i, idx);
+        float acc = 0.f;
+        if (idx < cnt) {
+          if (i != q_row) load_q(i);
+          const float* krow = K + (size_t)((unsigned long long)j * ldk);
+#pragma unroll
+          for (int v = 0; v < VEC; v++)
+            if (col_ok[v]) acc = dot4(q[v], ldg4(krow + v * G * 4), acc);
+        }
+        // part[] is indexed with compile-time constants only: scatter through a select chain
+#pragma unroll
+        for (int x = 0; x < G; x++) part[x] = (x == t) ? acc : part[x];
       }
     }
-    const int my_idx = l * NG + g;
-    const float s = __shfl_sync(FULL, my_s, my_idx);
-    if (my_idx < cnt) out[p0 + my_idx] = s * my_res;
+    transpose_reduce<G>(part, lane);
+    if (lane < cnt) out[p0 + lane] = my_s * part[0];
   }
 }
 
@@ -167,7 +205,10 @@ template <int G, int VEC>
 static int launch_sddmm(const SddmmArgs& a, int64_t batch, cudaStream_t st) {
   const long long spans = ceil_div(a.nnz, 32 * kChunksPerWarp);
   dim3 grid((unsigned)ceil_div(spans, kSddmmWarps), (unsigned)batch);
-  sddmm_kernel<G, VEC><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  if (a.d == G * VEC * 4)
+    sddmm_kernel<G, VEC, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  else
+    sddmm_kernel<G, VEC, false><<<grid, kSddmmWarps * 32, 0, st>>>(a);
   SB_LAUNCH_CHECK("sddmm_kernel");
   return SB_OK;
 }
@@ -176,17 +217,18 @@ static int sddmm_dispatch(SddmmArgs a, int64_t batch, cudaStream_t st) {
   if (a.nnz == 0) return SB_OK;
   const bool vec_ok = (a.d % 4 == 0) && (a.ldq % 4 == 0) && (a.ldk % 4 == 0) && aligned16(a.Q) &&
                       aligned16(a.K) && (a.stride_q % 4 == 0) && (a.stride_k % 4 == 0) &&
-                      a.d <= 512;
+                      a.d <= 512 && a.ldq < (1ll << 32) && a.ldk < (1ll << 32);
   if (!vec_ok) {
     dim3 grid((unsigned)ceil_div(a.nnz, 256), (unsigned)batch);
     sddmm_generic_kernel<<<grid, 256, 0, st>>>(a);
     SB_LAUNCH_CHECK("sddmm_generic_kernel");
     return SB_OK;
   }
-  // G lanes share one dot product, each holding VEC float4 of the Q row (G*VEC*4 >= d)
+  // G lanes share one dot product, each holding VEC float4 of the Q row (G*VEC*4 >= d); G
+  // adjacent lanes read G*16 contiguous bytes of a K row, i.e. whole 128-byte lines for d >= 32.
   if (a.d <= 16) return launch_sddmm<4, 1>(a, batch, st);
-  if (a.d <= 32) return launch_sddmm<4, 2>(a, batch, st);
-  if (a.d <= 64) return launch_sddmm<4, 4>(a, batch, st);
+  if (a.d <= 32) return launch_sddmm<8, 1>(a, batch, st);
+  if (a.d <= 64) return launch_sddmm<8, 2>(a, batch, st);
   if (a.d <= 128) return launch_sddmm<8, 4>(a, batch, st);
   if (a.d <= 256) return launch_sddmm<16, 4>(a, batch, st);
   return launch_sddmm<32, 4>(a, batch, st);
