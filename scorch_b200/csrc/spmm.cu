@@ -33,13 +33,52 @@ struct SpmmArgs {
   int skip_heavy;  // rows longer than SB_HEAVY_ROW_NNZ are left to the heavy kernels
 };
 
+// W floats (4 = 128-bit, 8 = 256-bit) moved by one load/store instruction.
+template <int W>
+struct Pack {
+  float v[W];
+};
+
+// Gather of a dense-operand row slice through the read-only path.  (An L2 evict-last policy on
+// these loads was measured on the 4096-column configuration and lost 25 %: left out.)
+template <int W>
+__device__ __forceinline__ Pack<W> ld_dense(const float* p) {
+  Pack<W> r;
+  if constexpr (W == 8) {
+    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]),
+                   "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+                 : "l"(p));
+  } else {
+    asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3])
+                 : "l"(p));
+  }
+  return r;
+}
+
+// Streaming (evict-first) store of an output slice: written once, never re-read here.
+template <int W>
+__device__ __forceinline__ void st_stream(float* p, const Pack<W>& r) {
+  if constexpr (W == 8)
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(r.v[0]),
+                 "f"(r.v[1]), "f"(r.v[2]), "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]),
+                 "f"(r.v[7])
+                 : "memory");
+  else
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(r.v[0]), "f"(r.v[1]),
+                 "f"(r.v[2]), "f"(r.v[3])
+                 : "memory");
+}
+
 // Accumulate entries [b, e) of one row into acc[] for this lane's columns.
-// L lanes per group, G = 32/L groups; group g takes entries b+g, b+g+G, ...
-template <int L, int VEC>
-__device__ __forceinline__ void accumulate_range(float4 (&acc)[VEC], const int* __restrict__ crd,
+// L lanes per group (each lane VEC packs of W floats, pack v at column (l + v*L)*W of the tile),
+// G = 32/L groups; group g takes entries b+g, b+g+G, ...  EXACT: the tile has no ragged edge.
+template <int L, int VEC, int W, bool EXACT>
+__device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int* __restrict__ crd,
                                                  const float* __restrict__ val,
-                                                 const float* __restrict__ Bcol, long long ldb,
-                                                 int b, int e, int lane, bool col_ok[VEC]) {
+                                                 const float* __restrict__ Bcol, unsigned ldb,
+                                                 int b, int e, int lane, const bool (&col_ok)[VEC]) {
   constexpr int G = 32 / L;
   const int g = lane / L;
   // software pipeline: the next chunk's indices/values are in flight while this chunk's rows of
@@ -60,80 +99,91 @@ __device__ __forceinline__ void accumulate_range(float4 (&acc)[VEC], const int* 
     }
     if (cnt == 32) {
       constexpr int STEPS = 32 / G;
-      constexpr int U = (STEPS >= 8) ? 8 : STEPS;
+      constexpr int UMAX = 32 / (VEC * W);  // about 32 floats (128 bytes) in flight per lane
+      constexpr int U = (STEPS < UMAX) ? STEPS : UMAX;
 #pragma unroll 1
       for (int s0 = 0; s0 < STEPS; s0 += U) {
-        int j[U];
         float a[U];
-        float4 bv[U][VEC];
+        Pack<W> bv[U][VEC];
 #pragma unroll
         for (int u = 0; u < U; u++) {
           const int t = (s0 + u) * G + g;
-          j[u] = __shfl_sync(FULL, my_j, t);
+          const unsigned j = (unsigned)__shfl_sync(FULL, my_j, t);
           a[u] = __shfl_sync(FULL, my_a, t);
+          const float* brow = Bcol + (size_t)((unsigned long long)j * ldb);
+#pragma unroll
+          for (int v = 0; v < VEC; v++) {
+            if (EXACT || col_ok[v]) {
+              bv[u][v] = ld_dense<W>(brow + v * L * W);
+            } else {
+#pragma unroll
+              for (int w = 0; w < W; w++) bv[u][v].v[w] = 0.f;
+            }
+          }
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
-          const float* brow = Bcol + (long long)j[u] * ldb;
 #pragma unroll
-          for (int v = 0; v < VEC; v++)
-            bv[u][v] = col_ok[v] ? ldg4(brow + v * L * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+          for (int v = 0; v < VEC; v++) {
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-#pragma unroll
-          for (int v = 0; v < VEC; v++) fma4(acc[v], a[u], bv[u][v]);
+            for (int w = 0; w < W; w++) acc[v].v[w] = fmaf(a[u], bv[u][v].v[w], acc[v].v[w]);
+          }
         }
       }
     } else {
       for (int t0 = 0; t0 < cnt; t0 += G) {
         const int t = t0 + g;
-        const int j = __shfl_sync(FULL, my_j, t & 31);
+        const unsigned j = (unsigned)__shfl_sync(FULL, my_j, t & 31);
         const float a = __shfl_sync(FULL, my_a, t & 31);
         if (t < cnt) {
-          const float* brow = Bcol + (long long)j * ldb;
+          const float* brow = Bcol + (size_t)((unsigned long long)j * ldb);
 #pragma unroll
-          for (int v = 0; v < VEC; v++)
-            if (col_ok[v]) fma4(acc[v], a, ldg4(brow + v * L * 4));
+          for (int v = 0; v < VEC; v++) {
+            if (EXACT || col_ok[v]) {
+              const Pack<W> x = ld_dense<W>(brow + v * L * W);
+#pragma unroll
+              for (int w = 0; w < W; w++) acc[v].v[w] = fmaf(a, x.v[w], acc[v].v[w]);
+            }
+          }
         }
       }
     }
   }
 }
 
-template <int L, int VEC>
-__device__ __forceinline__ void reduce_groups(float4 (&acc)[VEC]) {
+template <int L, int VEC, int W>
+__device__ __forceinline__ void reduce_groups(Pack<W> (&acc)[VEC]) {
 #pragma unroll
   for (int o = L; o < 32; o <<= 1) {
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
-      acc[v].x += __shfl_xor_sync(FULL, acc[v].x, o);
-      acc[v].y += __shfl_xor_sync(FULL, acc[v].y, o);
-      acc[v].z += __shfl_xor_sync(FULL, acc[v].z, o);
-      acc[v].w += __shfl_xor_sync(FULL, acc[v].w, o);
+#pragma unroll
+      for (int w = 0; w < W; w++) acc[v].v[w] += __shfl_xor_sync(FULL, acc[v].v[w], o);
     }
   }
 }
 
-__device__ __forceinline__ float4 epilogue(float4 s, const float* bias, int col, int relu) {
+template <int W>
+__device__ __forceinline__ Pack<W> epilogue(Pack<W> s, const float* bias, int col, int relu) {
   if (bias) {
-    const float4 bb = ldg4(bias + col);
-    s.x += bb.x; s.y += bb.y; s.z += bb.z; s.w += bb.w;
+#pragma unroll
+    for (int w = 0; w < W; w += 4) {
+      const float4 bb = ldg4(bias + col + w);
+      s.v[w] += bb.x; s.v[w + 1] += bb.y; s.v[w + 2] += bb.z; s.v[w + 3] += bb.w;
+    }
   }
   if (relu) {
-    s.x = s.x > 0.f ? s.x : 0.f;
-    s.y = s.y > 0.f ? s.y : 0.f;
-    s.z = s.z > 0.f ? s.z : 0.f;
-    s.w = s.w > 0.f ? s.w : 0.f;
+#pragma unroll
+    for (int w = 0; w < W; w++) s.v[w] = s.v[w] > 0.f ? s.v[w] : 0.f;
   }
   return s;
 }
 
 // One warp per row; grid = (row blocks, column tiles, batch).
-template <int L, int VEC>
+template <int L, int VEC, int W, bool EXACT>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 spmm_rows_kernel(SpmmArgs a) {
-  constexpr int TILE = L * 4 * VEC;
+  constexpr int TILE = L * W * VEC;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarpsPerCta + warp;
   if (row >= a.m) return;
@@ -141,23 +191,25 @@ spmm_rows_kernel(SpmmArgs a) {
   if (a.skip_heavy && e - b > SB_HEAVY_ROW_NNZ) return;
   const long long bz = blockIdx.z;
   const int l = lane % L;
-  const int col0 = blockIdx.y * TILE + l * 4;
+  const int col0 = blockIdx.y * TILE + l * W;
   bool col_ok[VEC];
-  float4 acc[VEC];
+  Pack<W> acc[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; v++) {
-    col_ok[v] = (col0 + v * L * 4) < a.k;
-    acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    col_ok[v] = EXACT || (col0 + v * L * W) < a.k;
+#pragma unroll
+    for (int w = 0; w < W; w++) acc[v].v[w] = 0.f;
   }
-  accumulate_range<L, VEC>(acc, a.crd, a.val + bz * a.stride_val, a.B + bz * a.stride_b + col0,
-                           a.ldb, b, e, lane, col_ok);
-  reduce_groups<L, VEC>(acc);
+  accumulate_range<L, VEC, W, EXACT>(acc, a.crd, a.val + bz * a.stride_val,
+                                           a.B + bz * a.stride_b + col0, (unsigned)a.ldb, b, e,
+                                           lane, col_ok);
+  reduce_groups<L, VEC, W>(acc);
   if (lane < L) {
     float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
-      const int col = col0 + v * L * 4;
-      if (col_ok[v]) st_stream4(crow + col, epilogue(acc[v], a.bias, col, a.relu));
+      const int col = col0 + v * L * W;
+      if (col_ok[v]) st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
     }
   }
 }
@@ -173,11 +225,11 @@ struct HeavyArgs {
 };
 
 // One CTA per heavy-row segment; grid = (segments, column tiles, batch).
-template <int L, int VEC>
+template <int L, int VEC, int W, bool EXACT>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
-  constexpr int TILE = L * 4 * VEC;
-  __shared__ float4 part[kWarpsPerCta][VEC][L];
+  constexpr int TILE = L * W * VEC;
+  __shared__ Pack<W> part[kWarpsPerCta][VEC][L];
   const int seg = blockIdx.x;
   if (seg >= __ldg(h.hdr + 1)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,20 +242,22 @@ spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
   const int se = min(re, sb_ + SB_HEAVY_ROW_NNZ);
   const long long bz = blockIdx.z;
   const int l = lane % L;
-  const int col0 = blockIdx.y * TILE + l * 4;
+  const int col0 = blockIdx.y * TILE + l * W;
   bool col_ok[VEC];
-  float4 acc[VEC];
+  Pack<W> acc[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; v++) {
-    col_ok[v] = (col0 + v * L * 4) < a.k;
-    acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    col_ok[v] = EXACT || (col0 + v * L * W) < a.k;
+#pragma unroll
+    for (int w = 0; w < W; w++) acc[v].v[w] = 0.f;
   }
   // each warp owns a contiguous slice of the segment (a multiple of 32 entries)
   constexpr int SLICE = SB_HEAVY_ROW_NNZ / kWarpsPerCta;
   const int wb = min(se, sb_ + warp * SLICE), we = min(se, wb + SLICE);
-  accumulate_range<L, VEC>(acc, a.crd, a.val + bz * a.stride_val, a.B + bz * a.stride_b + col0,
-                           a.ldb, wb, we, lane, col_ok);
-  reduce_groups<L, VEC>(acc);
+  accumulate_range<L, VEC, W, EXACT>(acc, a.crd, a.val + bz * a.stride_val,
+                                           a.B + bz * a.stride_b + col0, (unsigned)a.ldb, wb, we,
+                                           lane, col_ok);
+  reduce_groups<L, VEC, W>(acc);
   if (lane < L) {
 #pragma unroll
     for (int v = 0; v < VEC; v++) part[warp][v][l] = acc[v];
@@ -212,20 +266,23 @@ spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
   if (warp == 0 && lane < L) {
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
-      float4 s = part[0][v][l];
+      Pack<W> s = part[0][v][l];
 #pragma unroll
-      for (int w = 1; w < kWarpsPerCta; w++) {
-        const float4 t = part[w][v][l];
-        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+      for (int w2 = 1; w2 < kWarpsPerCta; w2++) {
+        const Pack<W> t = part[w2][v][l];
+#pragma unroll
+        for (int w = 0; w < W; w++) s.v[w] += t.v[w];
       }
-      const int col = col0 + v * L * 4;
+      const int col = col0 + v * L * W;
       if (!col_ok[v]) continue;
       if (nseg == 1) {
-        st_stream4(a.C + bz * a.stride_c + (long long)row * a.ldc + col,
-                   epilogue(s, a.bias, col, a.relu));
+        st_stream<W>(a.C + bz * a.stride_c + (long long)row * a.ldc + col,
+                     epilogue<W>(s, a.bias, col, a.relu));
       } else {
         float* dst = h.scratch + bz * h.scratch_batch + (long long)seg * a.k + col;
-        *reinterpret_cast<float4*>(dst) = s;
+#pragma unroll
+        for (int w = 0; w < W; w += 4)
+          *reinterpret_cast<float4*>(dst + w) = make_float4(s.v[w], s.v[w + 1], s.v[w + 2], s.v[w + 3]);
       }
     }
   }
@@ -244,12 +301,13 @@ __global__ void spmm_heavy_finalize_kernel(SpmmArgs a, HeavyArgs h) {
   const float* src = h.scratch + bz * h.scratch_batch + (long long)seg0 * a.k;
   float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
   for (int col = threadIdx.x * 4; col < a.k; col += blockDim.x * 4) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    Pack<4> s;
+    s.v[0] = s.v[1] = s.v[2] = s.v[3] = 0.f;
     for (int t = 0; t < nseg; t++) {
       const float4 v = *reinterpret_cast<const float4*>(src + (long long)t * a.k + col);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      s.v[0] += v.x; s.v[1] += v.y; s.v[2] += v.z; s.v[3] += v.w;
     }
-    st_stream4(crow + col, epilogue(s, a.bias, col, a.relu));
+    st_stream<4>(crow + col, epilogue<4>(s, a.bias, col, a.relu));
   }
 }
 
@@ -278,13 +336,13 @@ spmm_generic_kernel(int m, int k, const int* __restrict__ pos, const int* __rest
   C[(long long)row * ldc + col] = acc;
 }
 
-template <int L, int VEC>
-static int launch_vec(const SpmmArgs& a, int64_t batch, const void* plan, int64_t nnz,
-                      int64_t plan_segments, void* scratch, cudaStream_t st) {
-  constexpr int TILE = L * 4 * VEC;
+template <int L, int VEC, int W, bool EXACT>
+static int launch_vec2(const SpmmArgs& a, int64_t batch, const void* plan, int64_t nnz,
+                       int64_t plan_segments, void* scratch, cudaStream_t st) {
+  constexpr int TILE = L * W * VEC;
   const unsigned tiles = (unsigned)ceil_div(a.k, TILE);
   dim3 grid((unsigned)ceil_div(a.m, kWarpsPerCta), tiles, (unsigned)batch);
-  spmm_rows_kernel<L, VEC><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  spmm_rows_kernel<L, VEC, W, EXACT><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
   SB_LAUNCH_CHECK("spmm_rows_kernel");
   if (plan && plan_segments != 0) {
     PlanView pv = plan_view(plan, nnz);
@@ -292,7 +350,7 @@ static int launch_vec(const SpmmArgs& a, int64_t batch, const void* plan, int64_
     HeavyArgs h{pv.hdr, pv.heavy_row, pv.heavy_seg0, pv.heavy_nseg, pv.seg_heavy,
                 static_cast<float*>(scratch), (long long)segs * a.k};
     dim3 hg((unsigned)segs, tiles, (unsigned)batch);
-    spmm_heavy_kernel<L, VEC><<<hg, kWarpsPerCta * 32, 0, st>>>(a, h);
+    spmm_heavy_kernel<L, VEC, W, EXACT><<<hg, kWarpsPerCta * 32, 0, st>>>(a, h);
     SB_LAUNCH_CHECK("spmm_heavy_kernel");
     const int64_t heavy_bound = segs < pv.cap_heavy ? segs : pv.cap_heavy;
     dim3 fg((unsigned)heavy_bound, 1, (unsigned)batch);
@@ -301,6 +359,14 @@ static int launch_vec(const SpmmArgs& a, int64_t batch, const void* plan, int64_
     SB_LAUNCH_CHECK("spmm_heavy_finalize_kernel");
   }
   return SB_OK;
+}
+
+template <int L, int VEC, int W>
+static int launch_vec(const SpmmArgs& a, int64_t batch, const void* plan, int64_t nnz,
+                      int64_t plan_segments, void* scratch, cudaStream_t st) {
+  if (a.k % (L * W * VEC) == 0)
+    return launch_vec2<L, VEC, W, true>(a, batch, plan, nnz, plan_segments, scratch, st);
+  return launch_vec2<L, VEC, W, false>(a, batch, plan, nnz, plan_segments, scratch, st);
 }
 
 template <typename T>
@@ -356,7 +422,7 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
 
   const bool vec_ok = (k % 4 == 0) && (ldb % 4 == 0) && (ldc % 4 == 0) && aligned16(B) &&
                       aligned16(C) && (!bias || aligned16(bias)) && (stride_b % 4 == 0) &&
-                      (stride_c % 4 == 0);
+                      (stride_c % 4 == 0) && ldb < (1ll << 32);
   if (!vec_ok) {
     return launch_generic<float>(m, k, pos, crd, val, B, ldb, bias, relu, C, ldc, batch,
                                  stride_val, stride_b, stride_c, st);
@@ -376,12 +442,26 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
   a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
   a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
   a.skip_heavy = (plan && plan_segments != 0) ? 1 : 0;
-  if (k <= 16) return launch_vec<4, 1>(a, batch, plan, nnz, plan_segments, scratch, st);
-  if (k <= 32) return launch_vec<8, 1>(a, batch, plan, nnz, plan_segments, scratch, st);
-  if (k <= 64) return launch_vec<16, 1>(a, batch, plan, nnz, plan_segments, scratch, st);
-  if (k <= 128) return launch_vec<32, 1>(a, batch, plan, nnz, plan_segments, scratch, st);
-  if (k <= 256) return launch_vec<32, 2>(a, batch, plan, nnz, plan_segments, scratch, st);
-  return launch_vec<32, 4>(a, batch, plan, nnz, plan_segments, scratch, st);
+  // 256-bit loads (8 floats per lane) when every row slice is 32-byte aligned, else 128-bit.
+  const bool wide_ok = (k % 8 == 0) && (ldb % 8 == 0) && (ldc % 8 == 0) && (stride_b % 8 == 0) &&
+                       (stride_c % 8 == 0) && ((reinterpret_cast<uintptr_t>(B) & 31u) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(C) & 31u) == 0);
+#define SB_GO(L, VEC, W) \
+  return launch_vec<L, VEC, W>(a, batch, plan, nnz, plan_segments, scratch, st)
+  if (wide_ok) {
+    if (k <= 32) SB_GO(4, 1, 8);
+    if (k <= 64) SB_GO(8, 1, 8);
+    if (k <= 128) SB_GO(16, 1, 8);
+    // wider operands: 256-column panels on grid.y (a 32768-row panel = 32 MB stays in L2 while
+    // all row blocks pass over it; 128- and 512-column panels measured slower)
+    SB_GO(32, 1, 8);
+  }
+  if (k <= 16) SB_GO(4, 1, 4);
+  if (k <= 32) SB_GO(8, 1, 4);
+  if (k <= 64) SB_GO(16, 1, 4);
+  if (k <= 128) SB_GO(32, 1, 4);
+  SB_GO(32, 2, 4);
+#undef SB_GO
 }
 
 int sb_spmm_csr_typed(int dtype, int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
