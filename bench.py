@@ -43,9 +43,9 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) per launch of each kernel from ncu captures of this benchmark's
 # default workload, summarised under profiles/.  None = not captured yet.
 NCU_TRAFFIC_BYTES = {
-    "sddmm_kernel": None,
-    "csr_row_softmax_kernel": None,
-    "spmm_rows_kernel": None,
+    "sddmm_kernel": 329_144_064,            # profiles/c2_sparse_attention_kernels.md
+    "csr_row_softmax_kernel": 251_050_240,
+    "spmm_rows_kernel": 216_422_400,
 }
 
 
@@ -665,7 +665,8 @@ def main():
     achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "algorithmic_bytes_per_launch": alg[dom],
-                "launch_ms": stage_ms[dom], "traffic": NCU_TRAFFIC_BYTES.get(dom),
+                "launch_ms": stage_ms[dom],
+                "traffic": NCU_TRAFFIC_BYTES.get(dom) if args.workload == "c2" else None,
                 "per_kernel": {k: {"ms": stage_ms[k], "algorithmic_GBps": (alg[k] / (stage_ms[k] * 1e-3) / 1e9)
                                    if stage_ms[k] else None} for k in stage_ms}}
 

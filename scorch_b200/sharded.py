@@ -120,6 +120,15 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
             comm = shard._buffers["comm_stream"] = torch.cuda.Stream(device=dev)
     main = torch.cuda.current_stream(dev) if on_gpu else None
 
+    def mark(stream):
+        if timings is None or not on_gpu:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream)
+        return ev
+
+    if timings is not None:
+        timings.setdefault("events", []).append(("layer_start", mark(main)))
     recv, ready = [], []
     for idx, (c, w) in enumerate(panels):
         send = shard.buffer(f"send{idx}", (shard.max_rows, w), dev)
@@ -127,6 +136,8 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
             torch.matmul(x_local, weight[:, c:c + w], out=send[:rows])
         else:
             send[:rows].copy_(x_local[:, c:c + w])
+        if timings is not None:
+            timings["events"].append((f"transform{idx}_done", mark(main)))
         if world == 1:
             recv.append(send)
             ready.append(None)
@@ -137,7 +148,11 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
             produced.record(main)
             with torch.cuda.stream(comm):
                 comm.wait_event(produced)
+                if timings is not None:
+                    timings["events"].append((f"gather{idx}_start", mark(comm)))
                 dist.all_gather_into_tensor(buf, send, group=group)
+                if timings is not None:
+                    timings["events"].append((f"gather{idx}_done", mark(comm)))
                 done = torch.cuda.Event()
                 done.record(comm)
             ready.append(done)
@@ -148,15 +163,23 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
     for idx, (c, w) in enumerate(panels):
         if ready[idx] is not None:
             main.wait_event(ready[idx])
+        if timings is not None:
+            timings["events"].append((f"spmm{idx}_start", mark(main)))
         spmm_fn(shard, recv[idx], out[:, c:c + w], relu)
+        if timings is not None:
+            timings["events"].append((f"spmm{idx}_done", mark(main)))
     return out
 
 
 def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor,
-                        panel: int = 64, group=None, spmm_fn: Optional[Callable] = None) -> torch.Tensor:
-    """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329)."""
-    h = sharded_layer(shard, x_local, W1, relu=True, panel=panel, group=group, spmm_fn=spmm_fn)
-    return sharded_layer(shard, h, W2, relu=False, panel=panel, group=group, spmm_fn=spmm_fn)
+                        panel: int = 64, group=None, spmm_fn: Optional[Callable] = None,
+                        timings: Optional[dict] = None) -> torch.Tensor:
+    """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329).
+    ``timings``: optional dict that receives ("name", cuda event) pairs marking each phase."""
+    h = sharded_layer(shard, x_local, W1, relu=True, panel=panel, group=group, spmm_fn=spmm_fn,
+                      timings=timings)
+    return sharded_layer(shard, h, W2, relu=False, panel=panel, group=group, spmm_fn=spmm_fn,
+                         timings=timings)
 
 
 def gather_rows(shard: ShardedCsr, local: torch.Tensor, group=None) -> torch.Tensor:
