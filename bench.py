@@ -424,7 +424,7 @@ class GcnSharded:
         del X
         torch.cuda.empty_cache()
         self.W1, self.W2 = W.glorot(256, 256, seed=0, device="cuda"), W.glorot(256, 64, seed=1, device="cuda")
-        self.panel = None if self.world == 1 else 64
+        self.panel = None if self.world == 1 else "32,32,64,... (layer 1), 32,32 (layer 2)"
         self.host_x = self.X.cpu().pin_memory()
         self.stage_x = torch.empty_like(self.X)
         self.host_out = torch.empty((self.X.shape[0], 64), dtype=torch.float32).pin_memory()
@@ -459,8 +459,8 @@ class GcnSharded:
         self._ev.append((relu, a, b))
 
     def _forward(self, x, timed=False):
-        kw = dict(panel=self.panel or 10 ** 9, spmm_fn=self._spmm_timed if timed else None)
-        return self.S.gcn_forward_sharded(self.shard, x, self.W1, self.W2, **kw)
+        return self.S.gcn_forward_sharded(self.shard, x, self.W1, self.W2,
+                                          spmm_fn=self._spmm_timed if timed else None)
 
     def step(self, ev=None):
         self.out = self._forward(self.X, timed=ev is not None)

@@ -97,89 +97,139 @@ def _default_spmm(shard: ShardedCsr, B: torch.Tensor, out: torch.Tensor, relu: b
     K.spmm_csr(shard.pos, shard.crd, shard.val, B, relu=relu, plan=shard.plan, out=out)
 
 
+def _panels(k: int, widths) -> List[tuple]:
+    """(first column, width) of each column panel; ``widths`` is an int or a sequence that is
+    repeated/truncated to cover k columns."""
+    if isinstance(widths, int):
+        widths = [widths]
+    out, c, i = [], 0, 0
+    while c < k:
+        w = min(int(widths[min(i, len(widths) - 1)]), k - c)
+        out.append((c, w))
+        c += w
+        i += 1
+    return out
+
+
+class _Gatherer:
+    """Issues one panel's all-gather on the communication stream and hands back the event the
+    consumer has to wait for."""
+
+    def __init__(self, shard: ShardedCsr, dev, group):
+        self.shard, self.dev, self.group = shard, dev, group
+        self.on_gpu = dev.type == "cuda"
+        self.comm = None
+        if self.on_gpu and shard.world > 1:
+            self.comm = shard._buffers.get("comm_stream")
+            if self.comm is None:
+                self.comm = shard._buffers["comm_stream"] = torch.cuda.Stream(device=dev)
+        self.main = torch.cuda.current_stream(dev) if self.on_gpu else None
+
+    def gather(self, name: str, send: torch.Tensor):
+        """Returns (gathered buffer, event or None)."""
+        shard = self.shard
+        if shard.world == 1:
+            return send, None
+        buf = shard.buffer(name, (shard.world * shard.max_rows, send.shape[1]), self.dev)
+        if self.comm is None:
+            dist.all_gather_into_tensor(buf, send, group=self.group)
+            return buf, None
+        produced = torch.cuda.Event()
+        produced.record(self.main)
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(produced)
+            dist.all_gather_into_tensor(buf, send, group=self.group)
+            done = torch.cuda.Event()
+            done.record(self.comm)
+        return buf, done
+
+    def wait(self, event) -> None:
+        if event is not None:
+            self.main.wait_event(event)
+
+
 def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[torch.Tensor],
-                  relu: bool = False, panel: int = 64, group=None,
-                  spmm_fn: Optional[Callable] = None, timings: Optional[dict] = None) -> torch.Tensor:
+                  relu: bool = False, panel=64, group=None,
+                  spmm_fn: Optional[Callable] = None) -> torch.Tensor:
     """Rows [bounds[rank], bounds[rank+1]) of  act(A (X W))  (W = None: act(A X)).
 
     ``x_local`` holds this rank's rows of X.  Per column panel: local transform into the send
-    buffer, all-gather into the padded (world*max_rows, panel) receive buffer, SpMM of the local
-    row block over that panel.
+    buffer, all-gather into the padded (world*max_rows, panel) receive buffer on the
+    communication stream, SpMM of the local row block over that panel as soon as it has arrived.
     """
     spmm_fn = spmm_fn or _default_spmm
-    world, rows, dev = shard.world, shard.rows, x_local.device
+    rows, dev = shard.rows, x_local.device
     k = weight.shape[1] if weight is not None else x_local.shape[1]
-    panel = min(panel, k)
-    panels = [(c, min(panel, k - c)) for c in range(0, k, panel)]
+    panels = _panels(k, k if shard.world == 1 else panel)
     out = torch.empty((rows, k), dtype=torch.float32, device=dev)
-    on_gpu = x_local.is_cuda
-    comm = None
-    if on_gpu and world > 1:
-        comm = shard._buffers.get("comm_stream")
-        if comm is None:
-            comm = shard._buffers["comm_stream"] = torch.cuda.Stream(device=dev)
-    main = torch.cuda.current_stream(dev) if on_gpu else None
-
-    def mark(stream):
-        if timings is None or not on_gpu:
-            return None
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record(stream)
-        return ev
-
-    if timings is not None:
-        timings.setdefault("events", []).append(("layer_start", mark(main)))
-    recv, ready = [], []
+    g = _Gatherer(shard, dev, group)
+    pending = []
     for idx, (c, w) in enumerate(panels):
         send = shard.buffer(f"send{idx}", (shard.max_rows, w), dev)
         if weight is not None:
             torch.matmul(x_local, weight[:, c:c + w], out=send[:rows])
         else:
             send[:rows].copy_(x_local[:, c:c + w])
-        if timings is not None:
-            timings["events"].append((f"transform{idx}_done", mark(main)))
-        if world == 1:
-            recv.append(send)
-            ready.append(None)
-            continue
-        buf = shard.buffer(f"recv{idx}", (world * shard.max_rows, w), dev)
-        if comm is not None:
-            produced = torch.cuda.Event()
-            produced.record(main)
-            with torch.cuda.stream(comm):
-                comm.wait_event(produced)
-                if timings is not None:
-                    timings["events"].append((f"gather{idx}_start", mark(comm)))
-                dist.all_gather_into_tensor(buf, send, group=group)
-                if timings is not None:
-                    timings["events"].append((f"gather{idx}_done", mark(comm)))
-                done = torch.cuda.Event()
-                done.record(comm)
-            ready.append(done)
-        else:
-            dist.all_gather_into_tensor(buf, send, group=group)
-            ready.append(None)
-        recv.append(buf)
+        pending.append(g.gather(f"recv{idx}", send))
     for idx, (c, w) in enumerate(panels):
-        if ready[idx] is not None:
-            main.wait_event(ready[idx])
-        if timings is not None:
-            timings["events"].append((f"spmm{idx}_start", mark(main)))
-        spmm_fn(shard, recv[idx], out[:, c:c + w], relu)
-        if timings is not None:
-            timings["events"].append((f"spmm{idx}_done", mark(main)))
+        buf, ev = pending[idx]
+        g.wait(ev)
+        spmm_fn(shard, buf, out[:, c:c + w], relu)
     return out
 
 
 def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor,
-                        panel: int = 64, group=None, spmm_fn: Optional[Callable] = None,
-                        timings: Optional[dict] = None) -> torch.Tensor:
+                        panel=(32, 32, 64), panel2=32, group=None,
+                        spmm_fn: Optional[Callable] = None) -> torch.Tensor:
     """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329).
-    ``timings``: optional dict that receives ("name", cuda event) pairs marking each phase."""
-    h = sharded_layer(shard, x_local, W1, relu=True, panel=panel, group=group, spmm_fn=spmm_fn,
-                      timings=timings)
-    return sharded_layer(shard, h, W2, relu=False, panel=panel, group=group, spmm_fn=spmm_fn,
-                         timings=timings)
+
+    Both layers run as one pipeline so that as little communication as possible is exposed:
+      * layer 1 is cut into column panels (a narrow first one shortens the pipeline fill); panel
+        p's transform X W1[:, p] is all-gathered while the SpMM of panel p-1 runs;
+      * as soon as a panel of H = ReLU(A_hat ...) is final, its contribution H_p W2[p, :] is
+        accumulated into layer 2's send buffers, so after the last SpMM only a thin GEMM is left
+        before layer 2's gathers can start;
+      * layer 2 is cut into two panels so that the second gather overlaps the first SpMM.
+    With one rank there is nothing to gather and every layer is a single full-width SpMM.
+    """
+    spmm_fn = spmm_fn or _default_spmm
+    rows, dev, world = shard.rows, x_local.device, shard.world
+    k1, k2 = W1.shape[1], W2.shape[1]
+    if world == 1:
+        panel, panel2 = k1, k2
+    elif world == 2 and panel == (32, 32, 64) and panel2 == 32:
+        panel, panel2 = 64, k2   # two ranks: the gather hides behind SpMM anyway; wider panels are cheaper
+    p1, p2 = _panels(k1, panel), _panels(k2, panel2)
+    g = _Gatherer(shard, dev, group)
+    H = shard.buffer("hidden", (rows, k1), dev)
+    out = torch.empty((rows, k2), dtype=torch.float32, device=dev)
+
+    pending = []
+    for i, (c, w) in enumerate(p1):
+        send = shard.buffer(f"l1send{i}", (shard.max_rows, w), dev)
+        torch.matmul(x_local, W1[:, c:c + w], out=send[:rows])
+        pending.append(g.gather(f"l1recv{i}", send))
+    send2 = [shard.buffer(f"l2send{j}", (shard.max_rows, w), dev) for j, (_, w) in enumerate(p2)]
+    pending2 = []
+    for i, (c, w) in enumerate(p1):
+        buf, ev = pending[i]
+        g.wait(ev)
+        hp = H[:, c:c + w]
+        spmm_fn(shard, buf, hp, True)
+        last = i == len(p1) - 1
+        for j, (c2, w2) in enumerate(p2):
+            dst = send2[j][:rows]
+            if i == 0:
+                torch.matmul(hp, W2[c:c + w, c2:c2 + w2], out=dst)
+            else:
+                dst.addmm_(hp, W2[c:c + w, c2:c2 + w2])
+            if last:
+                pending2.append(g.gather(f"l2recv{j}", send2[j]))
+    for j, (c2, w2) in enumerate(p2):
+        buf, ev = pending2[j]
+        g.wait(ev)
+        spmm_fn(shard, buf, out[:, c2:c2 + w2], False)
+    return out
 
 
 def gather_rows(shard: ShardedCsr, local: torch.Tensor, group=None) -> torch.Tensor:

@@ -35,7 +35,7 @@ def _worker(rank, world, port, n, tmp):
         shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, world)
         r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
         for _ in range(2):  # twice: buffers and streams are reused across steps
-            out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, panel=64)
+            out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2)
         full = S.gather_rows(shard, out)
         torch.cuda.synchronize()
         if rank == 0:

@@ -38,7 +38,10 @@ def _worker(rank, world, port, n, tmp):
         W1, W2 = W.glorot(24, 40, seed=0), W.glorot(40, 8, seed=1)
         shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, world)
         r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
-        out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, panel=16, spmm_fn=_oracle_spmm)
+        out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, panel=(8, 16), panel2=4,
+                                    spmm_fn=_oracle_spmm)
+        one = S.sharded_layer(shard, X[r0:r1].contiguous(), W1, relu=True, panel=16, spmm_fn=_oracle_spmm)
+        assert one.shape == (r1 - r0, 40)
         full = S.gather_rows(shard, out)
         if rank == 0:
             torch.save({"out": full, "bounds": shard.bounds, "max_rows": shard.max_rows}, tmp)
