@@ -134,6 +134,8 @@ class SparseAttention:
         self.Q, self.Km, self.V = (t.cuda() for t in self.host)
         self.nnz = self.mask.nnz
         self.plan = K.CsrPlan(self.pos, self.nnz)
+        from scorch_b200 import pipelines as P
+        self.block_plan = None if os.environ.get("SCORCH_B200_NO_BLOCKS") else P.attention_block_plan(self.pos, self.crd)
         self.scores = torch.empty((self.units, self.nnz), dtype=torch.float32, device="cuda")
         self.out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, device="cuda")
         from scorch_b200 import pipelines as P
@@ -145,7 +147,10 @@ class SparseAttention:
 
     def config(self):
         return {"workload": self.name, "units_per_gpu": self.units, "seq": self.seq, "head_dim": self.d,
-                "mask_nnz": self.nnz, "l2": "inputs larger than L2 (Q,K,V,scores,mask = "
+                "mask_nnz": self.nnz,
+                "dense_16x16_blocks": self.block_plan.blocks if self.block_plan else 0,
+                "entries_outside_blocks": self.block_plan.rem_nnz if self.block_plan else self.nnz,
+                "l2": "inputs larger than L2 (Q,K,V,scores,mask = "
                 f"{(3 * self.units * self.seq * self.d * 4 + self.units * self.nnz * 4 + self.nnz * 8) >> 20} MiB)"}
 
     def alg_bytes(self):
@@ -163,18 +168,23 @@ class SparseAttention:
         if ev is not None:
             ev[0].record()
         # same calls as pipelines.sparse_attention, with preallocated outputs
-        s = K.sddmm_csr(self.pos, self.crd, self.mval, Q, Km, out=self.scores)
+        s = K.sddmm_csr(self.pos, self.crd, self.mval, Q, Km, out=self.scores, block_plan=self.block_plan)
         if ev is not None:
             ev[1].record()
         K.csr_row_softmax(self.pos, s, out=s)
         if ev is not None:
             ev[2].record()
-        K.spmm_csr(self.pos, self.crd, s, V, plan=self.plan, out=self.out)
+        K.spmm_csr(self.pos, self.crd, s, V, plan=self.plan, out=self.out, block_plan=self.block_plan)
         if ev is not None:
             ev[3].record()
 
+    # stage names; with a block plan the SDDMM and SpMM stages are two launches each
+    # (tensor-core kernel over the dense blocks + gather kernel over the remaining entries)
     kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
-    launches_per_step = 3
+
+    @property
+    def launches_per_step(self):
+        return 5 if self.block_plan else 3
 
     def step(self, ev=None):
         self._run(self.Q, self.Km, self.V, ev)

@@ -168,6 +168,36 @@ SB_API int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const 
                             int64_t stride_out, void* stream);
 
 /* --------------------------------------------------------------------------------------------
+ * Dense-block path (tensor cores) for patterns that contain dense aligned 16x16 blocks, e.g.
+ * banded attention masks.  A block plan splits the pattern once into its fully stored 16x16
+ * blocks and a CSR list of the remaining entries; the blocked SDDMM / SpMM run a TF32x3
+ * tensor-core kernel (fp32-level accuracy) over the blocks and the gather kernels over the rest.
+ * Results are identical in layout to the unblocked entry points (same entry order, same C).
+ * No counterpart in the reference: it has no block level type (src/scorch/format.py:7-11).
+ *   sb_block_plan_build : synchronises; returns the number of dense blocks and of remaining
+ *                         entries (blocks*256 + rem_nnz == nnz), which the blocked calls take back.
+ *   sb_sddmm_csr_blocked_f32 : d in {16, 32, 64, 128}; Q/K 16-byte aligned, pitches % 4 == 0;
+ *                              writes values only (no coordinate arrays).
+ *   sb_spmm_csr_blocked_f32  : k in {32, 64, 128}; for matrices without heavy rows.
+ * -------------------------------------------------------------------------------------------- */
+SB_API size_t sb_block_plan_bytes(int64_t m, int64_t nnz);
+SB_API int sb_block_plan_build(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                               const int32_t* crd, void* plan, size_t plan_bytes,
+                               int64_t* blocks_host, int64_t* rem_nnz_host, void* stream);
+SB_API int sb_sddmm_csr_blocked_f32(int64_t m, int64_t n, int64_t d, int64_t nnz,
+                                    const int32_t* pos, const int32_t* crd, const float* mask_val,
+                                    const float* Q, int64_t ldq, const float* K, int64_t ldk,
+                                    float* out_val, int64_t batch, int64_t stride_q,
+                                    int64_t stride_k, int64_t stride_out, const void* block_plan,
+                                    int64_t blocks, int64_t rem_nnz, void* stream);
+SB_API int sb_spmm_csr_blocked_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                                   const int32_t* crd, const float* val, const float* B,
+                                   int64_t ldb, const float* bias, int relu, float* C, int64_t ldc,
+                                   int64_t batch, int64_t stride_val, int64_t stride_b,
+                                   int64_t stride_c, const void* block_plan, int64_t blocks,
+                                   int64_t rem_nnz, void* stream);
+
+/* --------------------------------------------------------------------------------------------
  * Row softmax over the stored entries of a CSR matrix: out[p] = exp(scale*v[p] - max_row) / sum.
  * Rows without entries are untouched.  in == out is allowed.
  * Replaces: the caller-side torch scatter code between SDDMM and SpMM,

@@ -41,6 +41,14 @@ SIGNATURES = {
                                 _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "sb_sddmm_coo_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64,
                                 _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "sb_block_plan_bytes": (_sz, [_i64, _i64]),
+    "sb_block_plan_build": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _sz, C.POINTER(_i64),
+                                   C.POINTER(_i64), _ptr]),
+    "sb_sddmm_csr_blocked_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
+                                        _i64, _ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _i64, _ptr]),
+    "sb_spmm_csr_blocked_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
+                                       _int, _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _i64,
+                                       _ptr]),
     "sb_csr_row_softmax_f32": (_int, [_i64, _i64, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr]),
     "sb_spgemm_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "sb_spgemm_symbolic": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr,

@@ -61,6 +61,11 @@ int64_t plan_cap_heavy(int64_t nnz);
 int64_t plan_cap_seg(int64_t nnz);
 PlanView plan_view(const void* plan, int64_t nnz);
 
+// Exclusive scan of n int counts into out[0..n]; total (int64) at *total_dev; block_sum holds
+// ceil(n / 4096) + 1 int64 temporaries.  Defined in spgemm.cu.
+int exclusive_scan_i32(int n, const int* cnt, int* out, long long* block_sum, long long* total_dev,
+                       cudaStream_t st);
+
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__
 

@@ -24,6 +24,8 @@ struct SddmmArgs {
   const int* pos;   // CSR mask (null for COO)
   const int* row;   // COO mask (null for CSR)
   const int* crd;
+  const int* ent;         // optional entry list: entry q of this launch is entry ent[q] of crd /
+                          // mask_val / out_val (pos then describes the listed entries per row)
   const float* mask_val;  // may be null
   const float* Q;
   long long ldq;
@@ -108,11 +110,13 @@ sddmm_kernel(SddmmArgs a) {
   // software pipeline: the next chunk's entries are in flight while this chunk's K rows are
   // gathered
   int next_j = 0, next_i = 0;
+  long long next_p = 0;
   float next_s = 1.f;
   if (p0 + lane < p_end) {
-    next_j = ld_stream(a.crd + p0 + lane);
-    if (a.mask_val) next_s = ld_stream(a.mask_val + p0 + lane);
-    if (a.row) next_i = ld_stream(a.row + p0 + lane);
+    next_p = a.ent ? (long long)ld_stream(a.ent + p0 + lane) : p0 + lane;
+    next_j = ld_stream(a.crd + next_p);
+    if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
+    if (a.row) next_i = ld_stream(a.row + next_p);
   }
 #pragma unroll 1
   for (; p0 < p_end; p0 += 32) {
@@ -120,10 +124,12 @@ sddmm_kernel(SddmmArgs a) {
     const int my_j = next_j;
     int my_i = next_i;
     const float my_s = next_s;
+    const long long my_p = next_p;
     if (p0 + 32 + lane < p_end) {
-      next_j = ld_stream(a.crd + p0 + 32 + lane);
-      if (a.mask_val) next_s = ld_stream(a.mask_val + p0 + 32 + lane);
-      if (a.row) next_i = ld_stream(a.row + p0 + 32 + lane);
+      next_p = a.ent ? (long long)ld_stream(a.ent + p0 + 32 + lane) : p0 + 32 + lane;
+      next_j = ld_stream(a.crd + next_p);
+      if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
+      if (a.row) next_i = ld_stream(a.row + next_p);
     }
     bool one_row = false;  // warp-uniform: every entry of the chunk lies in row r0
     if (a.pos) {
@@ -133,8 +139,8 @@ sddmm_kernel(SddmmArgs a) {
       if (!one_row) my_i = row_of_entry(a.pos, r0, a.m, (int)p0 + min(lane, cnt - 1));
     }
     if (bz == 0 && lane < cnt) {
-      if (a.out_row) a.out_row[p0 + lane] = my_i;
-      if (a.out_col) a.out_col[p0 + lane] = my_j;
+      if (a.out_row) a.out_row[my_p] = my_i;
+      if (a.out_col) a.out_col[my_p] = my_j;
     }
 
     float part[G];
@@ -179,7 +185,7 @@ sddmm_kernel(SddmmArgs a) {
       }
     }
     transpose_reduce<G>(part, lane);
-    if (lane < cnt) out[p0 + lane] = my_s * part[0];
+    if (lane < cnt) out[my_p] = my_s * part[0];
   }
 }
 
@@ -290,6 +296,18 @@ static int check_sddmm(int64_t m, int64_t n, int64_t d, int64_t nnz, const void*
   return SB_OK;
 }
 
+// The entries of a mask that lie outside its dense blocks (blocked.cu): same kernel, entries
+// taken through the list `rem_ent`, rows described by `rem_pos`.  The caller has checked that the
+// operands qualify for the vector path.
+int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, const int* rem_ent,
+                    const int* crd, const float* mask_val, const float* Q, int64_t ldq,
+                    const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,
+                    int64_t stride_k, int64_t stride_out, cudaStream_t st) {
+  SddmmArgs a{(int)m, (int)d, rem_nnz, rem_pos, nullptr, crd, rem_ent, mask_val, Q, ldq, K, ldk, out,
+              nullptr, nullptr, stride_q, stride_k, stride_out};
+  return sddmm_dispatch(a, batch, st);
+}
+
 }  // namespace sb
 
 using namespace sb;
@@ -304,7 +322,7 @@ int sb_sddmm_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, crd, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(pos, "sddmm_csr: pos is null");
-  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, nullptr, mask_val, Q, ldq, K, ldk, out_val,
               out_row, out_col, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }
@@ -316,7 +334,7 @@ int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, col, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(nnz == 0 || row, "sddmm_coo: row is null");
-  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, nullptr, mask_val, Q, ldq, K, ldk, out_val,
               nullptr, nullptr, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }

@@ -472,6 +472,25 @@ scan_write_kernel(int m, const int* __restrict__ cnt, const long long* __restric
   }
 }
 
+// Exclusive scan of n int counts into out[0..n] (int32), running total in int64 at *total_dev.
+// `block_sum` needs ceil(n / 4096) + 1 int64 slots.
+int exclusive_scan_i32(int n, const int* cnt, int* out, long long* block_sum, long long* total_dev,
+                       cudaStream_t st) {
+  if (n <= 0) {
+    SB_CUDA(cudaMemsetAsync(out, 0, 4, st));
+    SB_CUDA(cudaMemsetAsync(total_dev, 0, 8, st));
+    return SB_OK;
+  }
+  const int nb = (int)ceil_div(n, kScanTile);
+  scan_reduce_kernel<<<nb, 1024, 0, st>>>(n, cnt, block_sum);
+  SB_LAUNCH_CHECK("scan_reduce_kernel");
+  scan_blocks_kernel<<<1, 32, 0, st>>>(nb, block_sum, total_dev);
+  SB_LAUNCH_CHECK("scan_blocks_kernel");
+  scan_write_kernel<<<nb, 1024, 0, st>>>(n, cnt, block_sum, out);
+  SB_LAUNCH_CHECK("scan_write_kernel");
+  return SB_OK;
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 template <typename T, bool NUMERIC>
 static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, int64_t n,
@@ -576,13 +595,8 @@ int sb_spgemm_symbolic(int64_t m, int64_t kb, int64_t n, const int32_t* Apos, co
   CsrIn in{Apos, Acrd, nullptr, Bpos, Bcrd, nullptr};
   rc = launch_bins<float, false>(w, counts, m, n, in, nullptr, nullptr, nullptr, st);
   if (rc != SB_OK) return rc;
-  const int nb = (int)ceil_div(m, kScanTile);
-  scan_reduce_kernel<<<nb, 1024, 0, st>>>((int)m, w.row_cnt, w.block_sum);
-  SB_LAUNCH_CHECK("scan_reduce_kernel");
-  scan_blocks_kernel<<<1, 32, 0, st>>>(nb, w.block_sum, w.hdr + 5);
-  SB_LAUNCH_CHECK("scan_blocks_kernel");
-  scan_write_kernel<<<nb, 1024, 0, st>>>((int)m, w.row_cnt, w.block_sum, Cpos);
-  SB_LAUNCH_CHECK("scan_write_kernel");
+  rc = exclusive_scan_i32((int)m, w.row_cnt, Cpos, w.block_sum, w.hdr + 5, st);
+  if (rc != SB_OK) return rc;
   // keep the bin sizes in the workspace header for the numeric phase
   SB_CUDA(cudaMemcpyAsync(w.hdr, counts, sizeof(counts), cudaMemcpyHostToDevice, st));
   long long total = 0;

@@ -31,6 +31,8 @@ struct SpmmArgs {
   long long ldc;
   long long stride_val, stride_b, stride_c;
   int skip_heavy;  // rows longer than SB_HEAVY_ROW_NNZ are left to the heavy kernels
+  const int* ent;  // optional entry list: entry p of pos[] is entry ent[p] of crd / val
+  int accumulate;  // add to the existing contents of C (before bias / ReLU)
 };
 
 // W floats (4 = 128-bit, 8 = 256-bit) moved by one load/store instruction.
@@ -78,7 +80,8 @@ template <int L, int VEC, int W, bool EXACT>
 __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int* __restrict__ crd,
                                                  const float* __restrict__ val,
                                                  const float* __restrict__ Bcol, unsigned ldb,
-                                                 int b, int e, int lane, const bool (&col_ok)[VEC]) {
+                                                 int b, int e, int lane, const bool (&col_ok)[VEC],
+                                                 const int* __restrict__ ent = nullptr) {
   constexpr int G = 32 / L;
   const int g = lane / L;
   // software pipeline: the next chunk's indices/values are in flight while this chunk's rows of
@@ -86,16 +89,18 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
   int next_j = 0;
   float next_a = 0.f;
   if (b + lane < e) {
-    next_j = ld_stream(crd + b + lane);
-    next_a = ld_stream(val + b + lane);
+    const int x = ent ? ld_stream(ent + b + lane) : b + lane;
+    next_j = ld_stream(crd + x);
+    next_a = ld_stream(val + x);
   }
   for (int p0 = b; p0 < e; p0 += 32) {
     const int cnt = min(32, e - p0);
     const int my_j = next_j;
     const float my_a = next_a;
     if (p0 + 32 + lane < e) {
-      next_j = ld_stream(crd + p0 + 32 + lane);
-      next_a = ld_stream(val + p0 + 32 + lane);
+      const int x = ent ? ld_stream(ent + p0 + 32 + lane) : p0 + 32 + lane;
+      next_j = ld_stream(crd + x);
+      next_a = ld_stream(val + x);
     }
     if (cnt == 32) {
       constexpr int STEPS = 32 / G;
@@ -202,14 +207,22 @@ spmm_rows_kernel(SpmmArgs a) {
   }
   accumulate_range<L, VEC, W, EXACT>(acc, a.crd, a.val + bz * a.stride_val,
                                            a.B + bz * a.stride_b + col0, (unsigned)a.ldb, b, e,
-                                           lane, col_ok);
+                                           lane, col_ok, a.ent);
   reduce_groups<L, VEC, W>(acc);
   if (lane < L) {
     float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
       const int col = col0 + v * L * W;
-      if (col_ok[v]) st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
+      if (!col_ok[v]) continue;
+      if (a.accumulate) {
+#pragma unroll
+        for (int w = 0; w < W; w += 4) {
+          const float4 old = *reinterpret_cast<const float4*>(crow + col + w);
+          acc[v].v[w] += old.x; acc[v].v[w + 1] += old.y; acc[v].v[w + 2] += old.z; acc[v].v[w + 3] += old.w;
+        }
+      }
+      st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
     }
   }
 }
@@ -381,6 +394,49 @@ static int launch_generic(int64_t m, int64_t k, const int32_t* pos, const int32_
   return SB_OK;
 }
 
+// Picks the vector kernel for k and the operands' alignment (the caller has checked the 128-bit
+// requirements).
+static int spmm_vec_dispatch(const SpmmArgs& a, int64_t k, int64_t ldb, int64_t ldc, int64_t stride_b,
+                             int64_t stride_c, const float* B, const float* C, int64_t batch,
+                             const void* plan, int64_t nnz, int64_t plan_segments, void* scratch,
+                             cudaStream_t st) {
+  // 256-bit loads (8 floats per lane) when every row slice is 32-byte aligned, else 128-bit.
+  const bool wide_ok = (k % 8 == 0) && (ldb % 8 == 0) && (ldc % 8 == 0) && (stride_b % 8 == 0) &&
+                       (stride_c % 8 == 0) && ((reinterpret_cast<uintptr_t>(B) & 31u) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(C) & 31u) == 0);
+#define SB_GO(L, VEC, W) \
+  return launch_vec<L, VEC, W>(a, batch, plan, nnz, plan_segments, scratch, st)
+  if (wide_ok) {
+    if (k <= 32) SB_GO(4, 1, 8);
+    if (k <= 64) SB_GO(8, 1, 8);
+    if (k <= 128) SB_GO(16, 1, 8);
+    // wider operands: 256-column panels on grid.y (a 32768-row panel = 32 MB stays in L2 while
+    // all row blocks pass over it; 128- and 512-column panels measured slower)
+    SB_GO(32, 1, 8);
+  }
+  if (k <= 16) SB_GO(4, 1, 4);
+  if (k <= 32) SB_GO(8, 1, 4);
+  if (k <= 64) SB_GO(16, 1, 4);
+  if (k <= 128) SB_GO(32, 1, 4);
+  SB_GO(32, 2, 4);
+#undef SB_GO
+}
+
+// Rows of the entries outside the dense blocks of a block plan (blocked.cu): C += A_rem B, then
+// bias / ReLU.  Entries are taken through the list `rem_ent`; no heavy-row split (the blocked
+// path is only offered for matrices without heavy rows).
+int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent, const int* crd,
+                   const float* val, const float* B, int64_t ldb, const float* bias, int relu,
+                   float* C, int64_t ldc, int64_t batch, int64_t stride_val, int64_t stride_b,
+                   int64_t stride_c, cudaStream_t st) {
+  SpmmArgs a;
+  a.m = (int)m; a.k = (int)k; a.pos = rem_pos; a.crd = crd; a.val = val; a.B = B; a.ldb = ldb;
+  a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
+  a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
+  a.skip_heavy = 0; a.ent = rem_ent; a.accumulate = 1;
+  return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, nullptr, 0, 0, nullptr, st);
+}
+
 static int check_common(int64_t m, int64_t n, int64_t k, int64_t nnz, const void* pos,
                         const void* crd, const void* val, const void* B, int64_t ldb,
                         const void* C, int64_t ldc) {
@@ -442,26 +498,9 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
   a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
   a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
   a.skip_heavy = (plan && plan_segments != 0) ? 1 : 0;
-  // 256-bit loads (8 floats per lane) when every row slice is 32-byte aligned, else 128-bit.
-  const bool wide_ok = (k % 8 == 0) && (ldb % 8 == 0) && (ldc % 8 == 0) && (stride_b % 8 == 0) &&
-                       (stride_c % 8 == 0) && ((reinterpret_cast<uintptr_t>(B) & 31u) == 0) &&
-                       ((reinterpret_cast<uintptr_t>(C) & 31u) == 0);
-#define SB_GO(L, VEC, W) \
-  return launch_vec<L, VEC, W>(a, batch, plan, nnz, plan_segments, scratch, st)
-  if (wide_ok) {
-    if (k <= 32) SB_GO(4, 1, 8);
-    if (k <= 64) SB_GO(8, 1, 8);
-    if (k <= 128) SB_GO(16, 1, 8);
-    // wider operands: 256-column panels on grid.y (a 32768-row panel = 32 MB stays in L2 while
-    // all row blocks pass over it; 128- and 512-column panels measured slower)
-    SB_GO(32, 1, 8);
-  }
-  if (k <= 16) SB_GO(4, 1, 4);
-  if (k <= 32) SB_GO(8, 1, 4);
-  if (k <= 64) SB_GO(16, 1, 4);
-  if (k <= 128) SB_GO(32, 1, 4);
-  SB_GO(32, 2, 4);
-#undef SB_GO
+  a.ent = nullptr;
+  a.accumulate = 0;
+  return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, plan, nnz, plan_segments, scratch, st);
 }
 
 int sb_spmm_csr_typed(int dtype, int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,

@@ -70,6 +70,43 @@ def plan_for(pos: torch.Tensor, nnz: int) -> CsrPlan:
     return plan
 
 
+class BlockPlan:
+    """Dense 16x16 blocks + remainder entries of one CSR pattern (depends on ``pos``/``crd`` only);
+    see include/scorch_b200.h.  ``dense_fraction`` tells whether the blocked kernels pay off."""
+
+    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, n: Optional[int] = None):
+        pos, crd = _dev(pos, torch.int32, "pos"), _dev(crd, torch.int32, "crd")
+        self.m, self.nnz = pos.numel() - 1, crd.numel()
+        L = _lib.lib()
+        nbytes = L.sb_block_plan_bytes(self.m, self.nnz)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=pos.device)
+        b, r = C.c_int64(0), C.c_int64(0)
+        with torch.cuda.device(pos.device):
+            check(L.sb_block_plan_build(self.m, self.m if n is None else n, self.nnz, pos.data_ptr(),
+                                        crd.data_ptr(), self.buf.data_ptr(), nbytes, C.byref(b),
+                                        C.byref(r), _stream()))
+        self.blocks, self.rem_nnz = int(b.value), int(r.value)
+
+    @property
+    def dense_fraction(self) -> float:
+        return (self.blocks * 256) / self.nnz if self.nnz else 0.0
+
+
+def block_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> BlockPlan:
+    """Block plan cached on the ``crd`` tensor object (rebuilt after in-place writes)."""
+    cached = getattr(crd, "_sb_block_plan", None)
+    if cached is not None and cached[0] == (pos._version, crd._version, pos.data_ptr()):
+        return cached[1]
+    plan = BlockPlan(pos, crd)
+    crd._sb_block_plan = ((pos._version, crd._version, pos.data_ptr()), plan)
+    return plan
+
+
+BLOCKED_MIN_DENSE_FRACTION = 0.5   # below this the gather kernels alone are used
+_BLOCKED_SDDMM_D = (16, 32, 64, 128)
+_BLOCKED_SPMM_K = (32, 64, 128)
+
+
 def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
     """2-D operand whose rows are contiguous; the row pitch (leading dimension) may exceed the width."""
     if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
@@ -78,7 +115,8 @@ def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[CsrPlan] = None,
-             out: Optional[torch.Tensor] = None, n: Optional[int] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, n: Optional[int] = None,
+             block_plan: Optional[BlockPlan] = None) -> torch.Tensor:
     """C = act(bias + A @ B) for CSR A.  ``B`` is (n, k) or (batch, n, k); ``val`` is (nnz,) —
     shared by all batch items — or (batch, nnz).  Returns (m, k) or (batch, m, k).
     2-D ``B`` / ``out`` may be column slices of wider row-major buffers (row pitch > k)."""
@@ -125,6 +163,15 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
     if plan is None:
         plan = plan_for(pos, nnz)
     L = _lib.lib()
+    if (block_plan is not None and block_plan.blocks > 0 and plan.segments == 0
+            and k in _BLOCKED_SPMM_K and ldb % 4 == 0 and ldc % 4 == 0):
+        with torch.cuda.device(B.device):
+            check(L.sb_spmm_csr_blocked_f32(m, nb if n is None else n, k, nnz, pos.data_ptr(),
+                                            crd.data_ptr(), val.data_ptr(), B.data_ptr(), ldb,
+                                            _ptr(bias), int(bool(relu)), out.data_ptr(), ldc, batch,
+                                            stride_val, nb * k, m * k, block_plan.buf.data_ptr(),
+                                            block_plan.blocks, block_plan.rem_nnz, _stream()))
+        return out
     sbytes = L.sb_spmm_csr_scratch_bytes(plan.segments, k, batch)
     scratch = plan.scratch(sbytes) if sbytes else None
     with torch.cuda.device(B.device):
@@ -191,7 +238,7 @@ def _qk(Q, K):
 
 
 def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
-              out: Optional[torch.Tensor] = None):
+              out: Optional[torch.Tensor] = None, block_plan: Optional[BlockPlan] = None):
     """out[p] = mask_val[p] * <Q[i_p], K[j_p]> over the entries of a CSR mask, entry order kept.
     Returns values (nnz,) or (batch, nnz); with ``want_coords`` also fresh int32 (row, col)."""
     pos = _dev(pos, torch.int32, "pos")
@@ -206,6 +253,13 @@ def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
     elif not (out.is_cuda and out.dtype == torch.float32 and out.is_contiguous()
               and tuple(out.shape) == shape):
         raise ValueError(f"out must be a contiguous float32 CUDA tensor of shape {shape}")
+    if block_plan is not None and block_plan.blocks > 0 and not want_coords and d in _BLOCKED_SDDMM_D:
+        with torch.cuda.device(Q.device):
+            check(_lib.lib().sb_sddmm_csr_blocked_f32(
+                m, K.shape[-2], d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val), Q.data_ptr(), d,
+                K.data_ptr(), d, out.data_ptr(), batch, Q.shape[-2] * d, K.shape[-2] * d, nnz,
+                block_plan.buf.data_ptr(), block_plan.blocks, block_plan.rem_nnz, _stream()))
+        return out
     row = col = None
     if want_coords:
         row = torch.empty(nnz, dtype=torch.int32, device=Q.device)

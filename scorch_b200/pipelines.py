@@ -19,16 +19,27 @@ import torch
 from . import kernels as K
 
 
+def attention_block_plan(pos: torch.Tensor, crd: torch.Tensor) -> Optional[K.BlockPlan]:
+    """The mask's block plan if enough of it sits in dense 16x16 blocks to use the tensor-core
+    kernels (band / window masks do; purely random masks do not), else None."""
+    bp = K.block_plan_for(pos, crd)
+    return bp if bp.dense_fraction >= K.BLOCKED_MIN_DENSE_FRACTION else None
+
+
 def sparse_attention(pos: torch.Tensor, crd: torch.Tensor, mask_val: Optional[torch.Tensor],
                      Q: torch.Tensor, Kmat: torch.Tensor, V: torch.Tensor, scale: float = 1.0,
-                     plan: Optional[K.CsrPlan] = None, scores_out: Optional[list] = None
-                     ) -> torch.Tensor:
-    """Q, K, V: (units, seq, d) with units = batch*heads.  Returns O (units, seq, d)."""
-    s = K.sddmm_csr(pos, crd, mask_val, Q, Kmat)          # (units, nnz)
-    K.csr_row_softmax(pos, s, scale=scale, out=s)         # in place
+                     plan: Optional[K.CsrPlan] = None, scores_out: Optional[list] = None,
+                     block_plan="auto") -> torch.Tensor:
+    """Q, K, V: (units, seq, d) with units = batch*heads.  Returns O (units, seq, d).
+    ``block_plan``: "auto" (use the dense-block kernels when the mask has enough dense blocks),
+    None (gather kernels only) or a ``kernels.BlockPlan``."""
+    if isinstance(block_plan, str):
+        block_plan = attention_block_plan(pos, crd)
+    s = K.sddmm_csr(pos, crd, mask_val, Q, Kmat, block_plan=block_plan)   # (units, nnz)
+    K.csr_row_softmax(pos, s, scale=scale, out=s)                         # in place
     if scores_out is not None:
         scores_out.append(s)
-    return K.spmm_csr(pos, crd, s, V, plan=plan)
+    return K.spmm_csr(pos, crd, s, V, plan=plan, block_plan=block_plan)
 
 
 def gcn_forward(pos, crd, val, X, W1, W2, plan: Optional[K.CsrPlan] = None) -> torch.Tensor:
@@ -50,6 +61,7 @@ class HostSparseAttention:
         self.pos, self.crd, self.mask_val, self.scale = pos, crd, mask_val, scale
         self.units, self.seq, self.d = units, seq, d
         self.plan = K.plan_for(pos, crd.numel())
+        self.block_plan = attention_block_plan(pos, crd)
         self.bounds = [units * c // chunks for c in range(chunks + 1)]
         self.dev = [torch.empty((units, seq, d), dtype=torch.float32, device=dev) for _ in range(3)]
         self.scores = torch.empty((units, crd.numel()), dtype=torch.float32, device=dev)
@@ -74,9 +86,10 @@ class HostSparseAttention:
                 arrived.record(self.s_in)
             main.wait_event(arrived)
             s = K.sddmm_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1], self.dev[1][u0:u1],
-                            out=self.scores[u0:u1])
+                            out=self.scores[u0:u1], block_plan=self.block_plan)
             K.csr_row_softmax(self.pos, s, scale=self.scale, out=s)
-            K.spmm_csr(self.pos, self.crd, s, self.dev[2][u0:u1], plan=self.plan, out=self.out[u0:u1])
+            K.spmm_csr(self.pos, self.crd, s, self.dev[2][u0:u1], plan=self.plan, out=self.out[u0:u1],
+                       block_plan=self.block_plan)
             computed = torch.cuda.Event()
             computed.record(main)
             with torch.cuda.stream(self.s_out):
