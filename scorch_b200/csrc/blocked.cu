@@ -229,17 +229,34 @@ sddmm_block_kernel(BlockArgs a, const float* __restrict__ Q, unsigned ldq,
     }
   }
 
-  for (int b = kb; b < ke; b++) {
+  // software pipeline over the row block's dense blocks: the K rows of block b+1 are in flight
+  // while block b is multiplied
+  float4 kf[2][D16], kn[2][D16];
+  auto load_k = [&](int b, float4 (&dst)[2][D16]) {
     const int j0 = __ldg(a.blk_col + b) * 16;
-    float c[2][4];
-#pragma unroll
-    for (int n = 0; n < 2; n++) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
-    float4 kf[2][D16];
 #pragma unroll
     for (int n = 0; n < 2; n++) {
       const float* krow = K + (size_t)((unsigned long long)(unsigned)(j0 + 8 * n + g) * ldk) + 4 * t;
 #pragma unroll
-      for (int q = 0; q < D16; q++) kf[n][q] = ldg4(krow + 16 * q);
+      for (int q = 0; q < D16; q++) dst[n][q] = ldg4(krow + 16 * q);
+    }
+  };
+  load_k(kb, kn);
+  for (int b = kb; b < ke; b++) {
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+#pragma unroll
+      for (int q = 0; q < D16; q++) kf[n][q] = kn[n][q];
+    }
+    const int p0 = __ldg(a.blk_ent + (long long)b * 16 + g);
+    const int p1 = __ldg(a.blk_ent + (long long)b * 16 + g + 8);
+    if (b + 1 < ke) load_k(b + 1, kn);
+    // main and cross terms accumulate separately: shorter dependent mma chains
+    float c[2][4], x[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+      c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+      x[n][0] = x[n][1] = x[n][2] = x[n][3] = 0.f;
     }
 #pragma unroll
     for (int q = 0; q < D16; q++) {
@@ -256,12 +273,12 @@ sddmm_block_kernel(BlockArgs a, const float* __restrict__ Q, unsigned ldq,
           unsigned bh0, bl0, bh1, bl1;
           split_tf32(k0, bh0, bl0);
           split_tf32(k1, bh1, bl1);
-          mma_3xtf32(c[n], ahi, alo, bh0, bh1, bl0, bl1);
+          mma_tf32(x[n], alo, bh0, bh1);
+          mma_tf32(x[n], ahi, bl0, bl1);
+          mma_tf32(c[n], ahi, bh0, bh1);
         }
       }
     }
-    const int p0 = __ldg(a.blk_ent + (long long)b * 16 + g);
-    const int p1 = __ldg(a.blk_ent + (long long)b * 16 + g + 8);
 #pragma unroll
     for (int n = 0; n < 2; n++) {
       const int col = 8 * n + 2 * t;
@@ -270,10 +287,10 @@ sddmm_block_kernel(BlockArgs a, const float* __restrict__ Q, unsigned ldq,
         s00 = __ldg(mask_val + p0 + col); s01 = __ldg(mask_val + p0 + col + 1);
         s10 = __ldg(mask_val + p1 + col); s11 = __ldg(mask_val + p1 + col + 1);
       }
-      out[p0 + col] = s00 * c[n][0];
-      out[p0 + col + 1] = s01 * c[n][1];
-      out[p1 + col] = s10 * c[n][2];
-      out[p1 + col + 1] = s11 * c[n][3];
+      out[p0 + col] = s00 * (c[n][0] + x[n][0]);
+      out[p0 + col + 1] = s01 * (c[n][1] + x[n][1]);
+      out[p1 + col] = s10 * (c[n][2] + x[n][2]);
+      out[p1 + col + 1] = s11 * (c[n][3] + x[n][3]);
     }
   }
 }
@@ -304,6 +321,7 @@ spmm_block_kernel(BlockArgs a, const float* __restrict__ val, const float* __res
 #pragma unroll
   for (int u = 0; u < KT; u++) c[u][0] = c[u][1] = c[u][2] = c[u][3] = 0.f;
 
+  // (prefetching the next block's operands was measured here and lost: 147 registers)
   for (int b = kb; b < ke; b++) {
     const int j0 = __ldg(a.blk_col + b) * 16;
     const int p0 = __ldg(a.blk_ent + (long long)b * 16 + g);

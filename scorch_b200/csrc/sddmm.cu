@@ -24,6 +24,7 @@ struct SddmmArgs {
   const int* pos;   // CSR mask (null for COO)
   const int* row;   // COO mask (null for CSR)
   const int* crd;
+  int rowwise;            // one warp per row of pos[] (short rows) instead of one per entry span
   const int* ent;         // optional entry list: entry q of this launch is entry ent[q] of crd /
                           // mask_val / out_val (pos then describes the listed entries per row)
   const float* mask_val;  // may be null
@@ -67,22 +68,63 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[G], int lane) {
   }
 }
 
+// Partial dot products of one chunk whose entries all share the Q row held in q[]: group entry
+// t of this lane's group goes to part[t].  RAGGED (last chunk of a row or span): entries beyond
+// cnt re-read the chunk's first K row, a valid address, and their result is never stored.
+template <int G, int VEC, int HALF, bool RAGGED>
+__device__ __forceinline__ void chunk_dots(float (&part)[G], const float4 (&q)[VEC], int my_j,
+                                           const float* __restrict__ K, unsigned ldk, int g0,
+                                           int cnt, const bool (&col_ok)[VEC]) {
+  const int j_first = RAGGED ? __shfl_sync(FULL, my_j, 0) : 0;
+#pragma unroll
+  for (int t0 = 0; t0 < G; t0 += HALF) {
+    float4 kv[HALF][VEC];
+#pragma unroll
+    for (int u = 0; u < HALF; u++) {
+      const int idx = g0 + t0 + u;
+      int j = __shfl_sync(FULL, my_j, idx);
+      if (RAGGED && idx >= cnt) j = j_first;
+      const float* krow = K + (size_t)((unsigned long long)(unsigned)j * ldk);
+#pragma unroll
+      for (int v = 0; v < VEC; v++)
+        kv[u][v] = col_ok[v] ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < HALF; u++) {
+      float acc = 0.f;
+#pragma unroll
+      for (int v = 0; v < VEC; v++) acc = dot4(q[v], kv[u][v], acc);
+      part[t0 + u] = acc;
+    }
+  }
+}
+
 // G lanes per dot product, VEC float4 of the Q/K row per lane (G*VEC*4 >= d; EXACT: == d, no
 // column predicates).  A 32-entry chunk is handled as 32/G groups of G consecutive entries: a
 // group gathers its G K rows (each row read by G adjacent lanes: whole 128-byte lines), forms G
 // partial dots per lane and transpose-reduces them, after which lane t of the warp owns entry t
 // of the chunk.  Full chunks that lie inside one mask row take a path without per-entry row
 // bookkeeping or predicates.
-template <int G, int VEC, bool EXACT>
+// ROWWISE: one warp per mask row instead of one per entry span (used for the short rows of a
+// block plan's remainder list, where spans would cross a row boundary in almost every chunk).
+template <int G, int VEC, bool EXACT, bool ROWWISE>
 __global__ void __launch_bounds__(kSddmmWarps * 32, (VEC >= 4 || G >= 32) ? 2 : 3)
 sddmm_kernel(SddmmArgs a) {
   // K rows gathered together: about 8 128-bit loads in flight per lane
   constexpr int HALF = (8 / VEC < G) ? (8 / VEC) : G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long span = (long long)blockIdx.x * kSddmmWarps + warp;
-  long long p0 = span * (32 * kChunksPerWarp);
-  if (p0 >= a.nnz) return;
-  const long long p_end = min(a.nnz, p0 + 32 * kChunksPerWarp);
+  long long p0, p_end;
+  if (ROWWISE) {
+    if (span >= a.m) return;
+    p0 = __ldg(a.pos + span);
+    p_end = __ldg(a.pos + span + 1);
+    if (p0 == p_end) return;
+  } else {
+    p0 = span * (32 * kChunksPerWarp);
+    if (p0 >= a.nnz) return;
+    p_end = min(a.nnz, p0 + 32 * kChunksPerWarp);
+  }
   const long long bz = blockIdx.y;
   const int g0 = (lane / G) * G, l = lane % G;  // first lane of my group, my slice of the row
   const float* Q = a.Q + bz * a.stride_q + l * 4;
@@ -97,7 +139,7 @@ sddmm_kernel(SddmmArgs a) {
 #pragma unroll
   for (int v = 0; v < VEC; v++) q[v] = make_float4(0.f, 0.f, 0.f, 0.f);
   int q_row = -1;
-  int r0 = a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0;
+  int r0 = ROWWISE ? (int)span : (a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0);
 
   auto load_q = [&](int row) {
     q_row = row;
@@ -131,8 +173,10 @@ sddmm_kernel(SddmmArgs a) {
       if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
       if (a.row) next_i = ld_stream(a.row + next_p);
     }
-    bool one_row = false;  // warp-uniform: every entry of the chunk lies in row r0
-    if (a.pos) {
+    bool one_row = ROWWISE;  // warp-uniform: every entry of the chunk lies in row r0
+    if (ROWWISE) {
+      my_i = r0;
+    } else if (a.pos) {
       r0 = advance_row(a.pos, a.m, r0, (int)p0);
       my_i = r0;
       one_row = __ldg(a.pos + r0 + 1) > (int)p0 + cnt - 1;
@@ -144,26 +188,13 @@ sddmm_kernel(SddmmArgs a) {
     }
 
     float part[G];
-    if (one_row && cnt == 32) {
+    if (one_row && (ROWWISE || cnt == 32)) {
+      // every entry of the chunk shares Q row r0
       if (r0 != q_row) load_q(r0);
-#pragma unroll
-      for (int t0 = 0; t0 < G; t0 += HALF) {
-        float4 kv[HALF][VEC];
-#pragma unroll
-        for (int u = 0; u < HALF; u++) {
-          const unsigned j = (unsigned)__shfl_sync(FULL, my_j, g0 + t0 + u);
-          const float* krow = K + (size_t)((unsigned long long)j * ldk);
-#pragma unroll
-          for (int v = 0; v < VEC; v++)
-            kv[u][v] = col_ok[v] ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int u = 0; u < HALF; u++) {
-          float acc = 0.f;
-#pragma unroll
-          for (int v = 0; v < VEC; v++) acc = dot4(q[v], kv[u][v], acc);
-          part[t0 + u] = acc;
-        }
+      if (!ROWWISE || cnt == 32) {
+        chunk_dots<G, VEC, HALF, false>(part, q, my_j, K, ldk, g0, 32, col_ok);
+      } else {
+        if constexpr (ROWWISE) chunk_dots<G, VEC, HALF, true>(part, q, my_j, K, ldk, g0, cnt, col_ok);
       }
     } else {
 #pragma unroll 1
@@ -209,12 +240,17 @@ __global__ void sddmm_generic_kernel(SddmmArgs a) {
 
 template <int G, int VEC>
 static int launch_sddmm(const SddmmArgs& a, int64_t batch, cudaStream_t st) {
-  const long long spans = ceil_div(a.nnz, 32 * kChunksPerWarp);
-  dim3 grid((unsigned)ceil_div(spans, kSddmmWarps), (unsigned)batch);
-  if (a.d == G * VEC * 4)
-    sddmm_kernel<G, VEC, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
-  else
-    sddmm_kernel<G, VEC, false><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  const bool exact = a.d == G * VEC * 4;
+  if (a.rowwise && a.pos) {
+    dim3 grid((unsigned)ceil_div(a.m, kSddmmWarps), (unsigned)batch);
+    if (exact) sddmm_kernel<G, VEC, true, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+    else sddmm_kernel<G, VEC, false, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  } else {
+    const long long spans = ceil_div(a.nnz, 32 * kChunksPerWarp);
+    dim3 grid((unsigned)ceil_div(spans, kSddmmWarps), (unsigned)batch);
+    if (exact) sddmm_kernel<G, VEC, true, false><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+    else sddmm_kernel<G, VEC, false, false><<<grid, kSddmmWarps * 32, 0, st>>>(a);
+  }
   SB_LAUNCH_CHECK("sddmm_kernel");
   return SB_OK;
 }
@@ -303,7 +339,7 @@ int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, c
                     const int* crd, const float* mask_val, const float* Q, int64_t ldq,
                     const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,
                     int64_t stride_k, int64_t stride_out, cudaStream_t st) {
-  SddmmArgs a{(int)m, (int)d, rem_nnz, rem_pos, nullptr, crd, rem_ent, mask_val, Q, ldq, K, ldk, out,
+  SddmmArgs a{(int)m, (int)d, rem_nnz, rem_pos, nullptr, crd, 1, rem_ent, mask_val, Q, ldq, K, ldk, out,
               nullptr, nullptr, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, st);
 }
@@ -322,7 +358,7 @@ int sb_sddmm_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, crd, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(pos, "sddmm_csr: pos is null");
-  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, nullptr, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, 0, nullptr, mask_val, Q, ldq, K, ldk, out_val,
               out_row, out_col, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }
@@ -334,7 +370,7 @@ int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, col, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(nnz == 0 || row, "sddmm_coo: row is null");
-  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, nullptr, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, 0, nullptr, mask_val, Q, ldq, K, ldk, out_val,
               nullptr, nullptr, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }
