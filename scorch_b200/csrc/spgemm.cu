@@ -4,10 +4,11 @@
 // length of the matching B row:
 //   bin 0  U <= 32      one warp per row, 64-slot hash set/accumulator in shared memory
 //   bin 1  U <= 128     one warp per row, 256 slots
-//   bin 2  U <= 1024    one 128-thread CTA per row, 2048 slots
-//   bin 3  U <= 8192    one 512-thread CTA per row, 16384 slots
-//   bin 4  U  > 8192    dense bitmap (+ dense accumulator) of n columns in the workspace, a
-//                       bounded pool of persistent CTAs walks these rows
+//   bin 2  U <= 512     one 128-thread CTA per row, 1024 slots
+//   bin 3  U <= 2048    one 256-thread CTA per row, 4096 slots
+//   bin 4  U <= 8192    one 512-thread CTA per row, 16384 slots
+//   bin 5  U  > 8192    dense bitmap (+ dense accumulator) of n columns in the workspace; the
+//                       rows' entries are spread over the GPU as (row, chunk) tasks
 // Hash bins: open addressing with atomicCAS on the column key (+ atomicAdd on the value), load
 // factor <= 0.5 by construction.  The numeric phase compacts each row's table in place and sorts
 // the occupied part in shared memory (bitonic) so columns come out ascending like the
@@ -21,12 +22,12 @@
 
 namespace sb {
 
-constexpr int kBins = 5;
+constexpr int kBins = 6;
 constexpr int kEmpty = INT_MAX;
 constexpr int kDenseWorkersMax = 296;  // 2 CTAs per SM on a 148-SM part
 constexpr size_t kDenseBudget = (size_t)4 << 30;
 
-// Workspace header (int64 words): [0..4] rows per bin, [5] total nnz of C, [6] dense workers.
+// Workspace header (int64 words): [0..5] rows per bin, [8] total nnz of C.
 struct WsLayout {
   long long* hdr;       // 16 int64
   int* bin_cursor;      // kBins ints (+ padding)
@@ -34,6 +35,7 @@ struct WsLayout {
   int* bin_rows;        // kBins * m ints
   int* row_cnt;         // m ints
   long long* block_sum; // scan temporaries
+  int* dense_ctl;       // task prefix, per-row done counters and queue of the dense bin
   unsigned* bitmap;     // workers * words
   void* dense_acc;      // workers * n * sizeof(T)
   int workers;
@@ -55,6 +57,7 @@ static WsLayout ws_layout(void* base, int64_t m, int64_t n, int dtype) {
   w.row_cnt = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4);
   w.block_sum = reinterpret_cast<long long*>(p + off);
   off += align_up((size_t)(ceil_div(m > 0 ? m : 1, 4096) + 1) * 8);
+  w.dense_ctl = reinterpret_cast<int*>(p + off); off += align_up((size_t)(2 * kDenseWorkersMax + 8) * 4);
   w.words = (n + 31) / 32;
   const size_t per_worker = (size_t)w.words * 4 + (size_t)n * dtype_size(dtype);
   long long workers = per_worker ? (long long)(kDenseBudget / per_worker) : kDenseWorkersMax;
@@ -71,9 +74,10 @@ static WsLayout ws_layout(void* base, int64_t m, int64_t n, int dtype) {
 __device__ __forceinline__ int bin_of(int u) {
   if (u <= 32) return 0;
   if (u <= 128) return 1;
-  if (u <= 1024) return 2;
-  if (u <= 8192) return 3;
-  return 4;
+  if (u <= 512) return 2;
+  if (u <= 2048) return 3;
+  if (u <= 8192) return 4;
+  return 5;
 }
 
 // 8 lanes per row of A: U_i and the row's bin; rows are appended to their bin's list with one
@@ -312,36 +316,117 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
   }
 }
 
-// Bin 4: persistent CTAs, each owning one bitmap (+ accumulator) of n columns in the workspace.
-// Both stay all-zero between rows: every set bit / touched sum is cleared while it is emitted.
+// Bin 4 (rows whose products do not fit a shared-memory table): dense bitmap (+ accumulator) of
+// n columns per row in the workspace.  Rows are handled in batches of up to `slots` rows, one
+// slot each; a row's A entries are cut into chunks of kDenseChunk entries and the (row, chunk)
+// tasks of a batch are handed out through an atomic queue, so a hub row with hundreds of
+// thousands of entries is spread over the whole GPU.  The CTA that finishes a row's last chunk
+// (a counter per row, no spinning) walks the row's bitmap in ascending column order, emits the
+// row and leaves bitmap and accumulator all-zero for the next batch.
+constexpr int kDenseChunk = 2048;     // A entries per task
+constexpr int kLongBRow = 4096;       // B rows at least this long are handled by the whole CTA
+constexpr int kDeferCap = 32;
+
+struct DenseCtl {
+  int* task_pref;  // [slots + 1]
+  int* done;       // [slots]
+  int* queue;      // [1]
+};
+
+__global__ void dense_batch_setup_kernel(const int* __restrict__ rows, int r0, int nb,
+                                         const int* __restrict__ Apos, DenseCtl ctl) {
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int k = 0; k < nb; k++) {
+      ctl.task_pref[k] = run;
+      const int i = rows[r0 + k];
+      const int len = Apos[i + 1] - Apos[i];
+      run += max(1, (len + kDenseChunk - 1) / kDenseChunk);
+      ctl.done[k] = 0;
+    }
+    ctl.task_pref[nb] = run;
+    *ctl.queue = 0;
+  }
+}
+
+template <typename T, bool NUMERIC>
+__device__ __forceinline__ void dense_add_brow(const CsrIn& in, int j, T a, unsigned* bitmap, T* acc,
+                                               int start, int stride) {
+  const T* Bval = static_cast<const T*>(in.Bval);
+  const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
+  for (int pb = bb + start; pb < be; pb += stride) {
+    const int c = __ldg(in.Bcrd + pb);
+    if (NUMERIC) atomicAdd(&acc[c], a * Bval[pb]);
+    atomicOr(&bitmap[c >> 5], 1u << (c & 31));
+  }
+}
+
 template <typename T, bool NUMERIC>
 __global__ void __launch_bounds__(256)
-spgemm_dense_kernel(const int* __restrict__ rows, int nrows, CsrIn in, long long words,
+spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long long words,
                     unsigned* __restrict__ bitmap_all, T* __restrict__ acc_all, long long n,
-                    int* __restrict__ row_cnt, const int* __restrict__ Cpos,
+                    DenseCtl ctl, int* __restrict__ row_cnt, const int* __restrict__ Cpos,
                     int* __restrict__ Ccrd, T* __restrict__ Cval) {
   __shared__ int s_warp[8];
   __shared__ int s_base;
-  unsigned* bitmap = bitmap_all + (long long)blockIdx.x * words;
-  T* acc = NUMERIC ? acc_all + (long long)blockIdx.x * n : nullptr;
+  __shared__ int s_task;
+  __shared__ int s_last;
+  __shared__ int s_ndefer;
+  __shared__ int s_defer[kDeferCap];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const T* Aval = static_cast<const T*>(in.Aval);
-  const T* Bval = static_cast<const T*>(in.Bval);
-  for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
-    const int i = __ldg(rows + r);
-    const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
-    for (int pa = ab + warp; pa < ae; pa += 8) {
-      const int j = __ldg(in.Acrd + pa);
-      T a = T(0);
-      if (NUMERIC) a = Aval[pa];
-      const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
-      for (int pb = bb + lane; pb < be; pb += 32) {
-        const int c = __ldg(in.Bcrd + pb);
-        if (NUMERIC) atomicAdd(&acc[c], a * Bval[pb]);
-        atomicOr(&bitmap[c >> 5], 1u << (c & 31));
-      }
+  const int total = __ldg(ctl.task_pref + nb);
+  while (true) {
+    if (tid == 0) {
+      s_task = atomicAdd(ctl.queue, 1);
+      s_ndefer = 0;
     }
     __syncthreads();
+    const int task = s_task;
+    if (task >= total) return;
+    // slot k with task_pref[k] <= task < task_pref[k+1]
+    int lo = 0, hi = nb;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(ctl.task_pref + mid) <= task) lo = mid; else hi = mid;
+    }
+    const int k = lo;
+    const int chunk = task - __ldg(ctl.task_pref + k);
+    const int nchunks = __ldg(ctl.task_pref + k + 1) - __ldg(ctl.task_pref + k);
+    const int i = __ldg(rows + r0 + k);
+    unsigned* bitmap = bitmap_all + (long long)k * words;
+    T* acc = NUMERIC ? acc_all + (long long)k * n : nullptr;
+    const int ab = __ldg(in.Apos + i) + chunk * kDenseChunk;
+    const int ae = min(__ldg(in.Apos + i + 1), ab + kDenseChunk);
+    // warps take A entries; long B rows are put aside for the whole CTA
+    for (int pa = ab + warp; pa < ae; pa += 8) {
+      const int j = __ldg(in.Acrd + pa);
+      const int blen = __ldg(in.Bpos + j + 1) - __ldg(in.Bpos + j);
+      bool mine = true;
+      if (blen >= kLongBRow) {
+        int slot = 0;
+        if (lane == 0) slot = atomicAdd(&s_ndefer, 1);
+        slot = __shfl_sync(FULL, slot, 0);
+        if (slot < kDeferCap) {
+          if (lane == 0) s_defer[slot] = pa;
+          mine = false;
+        }
+      }
+      if (mine) dense_add_brow<T, NUMERIC>(in, j, NUMERIC ? Aval[pa] : T(0), bitmap, acc, lane, 32);
+    }
+    __syncthreads();
+    const int nd = min(s_ndefer, kDeferCap);
+    for (int q = 0; q < nd; q++) {
+      const int pa = s_defer[q];
+      dense_add_brow<T, NUMERIC>(in, __ldg(in.Acrd + pa), NUMERIC ? Aval[pa] : T(0), bitmap, acc, tid, 256);
+    }
+    // publish this chunk, then find out whether it was the row's last one
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(ctl.done + k, 1) == nchunks - 1);
+    __syncthreads();
+    if (!s_last) continue;
+    __threadfence();
     // walk the bitmap in ascending order, 256 words per step
     if (tid == 0) s_base = 0;
     __syncthreads();
@@ -506,30 +591,32 @@ static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, in
         rows0 + m, (int)counts[1], in, w.row_cnt, Cpos, Ccrd, Cval);
     SB_LAUNCH_CHECK("spgemm_warp_kernel<256>");
   }
-  if (counts[2] > 0) {
-    constexpr int S = 2048;
-    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);
-    auto k = spgemm_cta_kernel<T, S, 128, NUMERIC>;
-    SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<(unsigned)counts[2], 128, smem, st>>>(rows0 + 2 * m, (int)counts[2], in, w.row_cnt, Cpos,
-                                             Ccrd, Cval);
-    SB_LAUNCH_CHECK("spgemm_cta_kernel<2048>");
+#define SB_CTA_BIN(IDX, SLOTS, THREADS)                                                        \
+  if (counts[IDX] > 0) {                                                                      \
+    constexpr int S = SLOTS;                                                                  \
+    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);                \
+    auto k = spgemm_cta_kernel<T, S, THREADS, NUMERIC>;                                       \
+    SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    k<<<(unsigned)counts[IDX], THREADS, smem, st>>>(rows0 + (long long)IDX * m, (int)counts[IDX], \
+                                                    in, w.row_cnt, Cpos, Ccrd, Cval);         \
+    SB_LAUNCH_CHECK("spgemm_cta_kernel");                                                     \
   }
-  if (counts[3] > 0) {
-    constexpr int S = 16384;
-    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);
-    auto k = spgemm_cta_kernel<T, S, 512, NUMERIC>;
-    SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<(unsigned)counts[3], 512, smem, st>>>(rows0 + 3 * m, (int)counts[3], in, w.row_cnt, Cpos,
-                                             Ccrd, Cval);
-    SB_LAUNCH_CHECK("spgemm_cta_kernel<16384>");
-  }
-  if (counts[4] > 0) {
-    const int workers = (int)(counts[4] < w.workers ? counts[4] : w.workers);
-    spgemm_dense_kernel<T, NUMERIC><<<workers, 256, 0, st>>>(
-        rows0 + 4 * m, (int)counts[4], in, w.words, w.bitmap, static_cast<T*>(w.dense_acc),
-        (long long)n, w.row_cnt, Cpos, Ccrd, Cval);
-    SB_LAUNCH_CHECK("spgemm_dense_kernel");
+  SB_CTA_BIN(2, 1024, 128)
+  SB_CTA_BIN(3, 4096, 256)
+  SB_CTA_BIN(4, 16384, 512)
+#undef SB_CTA_BIN
+  if (counts[5] > 0) {
+    DenseCtl ctl{w.dense_ctl, w.dense_ctl + kDenseWorkersMax + 1, w.dense_ctl + 2 * kDenseWorkersMax + 2};
+    const int grid = 4 * sm_count();
+    for (long long r0 = 0; r0 < counts[5]; r0 += w.workers) {
+      const int nb = (int)((counts[5] - r0) < w.workers ? (counts[5] - r0) : w.workers);
+      dense_batch_setup_kernel<<<1, 32, 0, st>>>(rows0 + 5 * m, (int)r0, nb, in.Apos, ctl);
+      SB_LAUNCH_CHECK("dense_batch_setup_kernel");
+      spgemm_dense_kernel<T, NUMERIC><<<grid, 256, 0, st>>>(
+          rows0 + 5 * m, (int)r0, nb, in, w.words, w.bitmap, static_cast<T*>(w.dense_acc),
+          (long long)n, ctl, w.row_cnt, Cpos, Ccrd, Cval);
+      SB_LAUNCH_CHECK("spgemm_dense_kernel");
+    }
   }
   return SB_OK;
 }
@@ -591,16 +678,16 @@ int sb_spgemm_symbolic(int64_t m, int64_t kb, int64_t n, const int32_t* Apos, co
   SB_CUDA(cudaStreamSynchronize(st));
   long long counts[kBins];
   for (int b = 0; b < kBins; b++) counts[b] = cursors[b];
-  if (counts[4] > 0) SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
+  if (counts[kBins - 1] > 0) SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
   CsrIn in{Apos, Acrd, nullptr, Bpos, Bcrd, nullptr};
   rc = launch_bins<float, false>(w, counts, m, n, in, nullptr, nullptr, nullptr, st);
   if (rc != SB_OK) return rc;
-  rc = exclusive_scan_i32((int)m, w.row_cnt, Cpos, w.block_sum, w.hdr + 5, st);
+  rc = exclusive_scan_i32((int)m, w.row_cnt, Cpos, w.block_sum, w.hdr + 8, st);
   if (rc != SB_OK) return rc;
   // keep the bin sizes in the workspace header for the numeric phase
   SB_CUDA(cudaMemcpyAsync(w.hdr, counts, sizeof(counts), cudaMemcpyHostToDevice, st));
   long long total = 0;
-  SB_CUDA(cudaMemcpyAsync(&total, w.hdr + 5, 8, cudaMemcpyDeviceToHost, st));
+  SB_CUDA(cudaMemcpyAsync(&total, w.hdr + 8, 8, cudaMemcpyDeviceToHost, st));
   SB_CUDA(cudaStreamSynchronize(st));
   *total_nnz_host = total;
   if (total > INT32_MAX)
@@ -633,7 +720,7 @@ int sb_spgemm_numeric(int dtype, int64_t m, int64_t kb, int64_t n, const int32_t
   SB_CHECK_ARG(binned <= m, "spgemm_numeric: workspace does not hold the bins of a symbolic call");
   if (binned == 0) return SB_OK;
   SB_CHECK_ARG(Ccrd && Cval && Aval && Bval, "spgemm_numeric: null pointer");
-  if (counts[4] > 0) {
+  if (counts[kBins - 1] > 0) {
     SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
     SB_CUDA(cudaMemsetAsync(w.dense_acc, 0, (size_t)w.workers * (size_t)n * dtype_size(dtype), st));
   }

@@ -342,7 +342,7 @@ def test_spgemm_all_bins_vs_oracle(oracle):
     pos, crd, val = A.pos.numpy(), A.crd.numpy(), A.val.numpy()
     lens = np.diff(pos)
     upper = np.add.reduceat(lens[crd], pos[:-1])  # every row has >= 1 entry
-    for lo, hi in ((1, 32), (33, 128), (129, 1024), (1025, 8192), (8193, 1 << 30)):
+    for lo, hi in ((1, 32), (33, 128), (129, 512), (513, 2048), (2049, 8192), (8193, 1 << 30)):
         assert ((upper >= lo) & (upper <= hi)).any(), f"no row with upper bound in [{lo},{hi}]"
     cpos, ccrd, cval = K.spgemm_csr(dev(pos), dev(crd), dev(val), dev(pos), dev(crd), dev(val), 60000)
     wpos, wcrd, _ = oracle.spgemm(pos, crd, val, pos, crd, val, 60000)
