@@ -52,13 +52,13 @@ SB_API const char* sb_status_string(int status);
 SB_API const char* sb_last_error(void);
 
 /* --------------------------------------------------------------------------------------------
- * Row plan: the nnz-balanced split of a CSR matrix that SpMM and SpMV use.  Rows with more than
+ * Row plan: the nnz-balanced split of a CSR matrix that SpMM uses.  Rows with more than
  * SB_HEAVY_ROW_NNZ stored entries ("heavy" rows, e.g. hubs of a power-law graph) are cut into
  * segments of SB_HEAVY_ROW_NNZ entries; one CTA sums one segment in shared memory and a
  * fixed-order second stage adds the segment sums, so results do not depend on scheduling.
  * The plan depends only on `pos`; build it once per matrix and reuse it.
  * Replaces: the atomic work-stealing row loop of csrc/spmm.h:2032-2046 and the
- * schedule(dynamic,16) / schedule(static) loops of csrc/spmm.h:121, csrc/kernels.h:32.
+ * schedule(dynamic,16) loop of csrc/spmm.h:121.
  * -------------------------------------------------------------------------------------------- */
 #define SB_HEAVY_ROW_NNZ 1024
 
@@ -114,13 +114,14 @@ SB_API int sb_spmm_csr_typed(int dtype, int64_t m, int64_t n, int64_t k, int64_t
  * CSR SpMV: y[i] = sum_p val[p] * x[crd[p]].  Every y[i] is written.
  * Replaces: spmv_csr<T> csrc/kernels.h:12-49 (prebuilt_spmv_csr_{f32,f64,i32,i64}) and the
  *           compiler-emitted loop of scorch.ops.spmv (src/scorch/ops.py:48-136).
- * The fp32 entry uses the row plan (may be NULL) and a scratch of sb_spmv_csr_scratch_bytes().
+ * The fp32 entry cuts the entry arrays into tiles (balanced by stored entries, so power-law rows
+ * need no special case) and takes a scratch of sb_spmv_csr_scratch_bytes(nnz) for the partial
+ * sums of rows cut by tile borders; they are added in tile order (bitwise reproducible).
  * -------------------------------------------------------------------------------------------- */
-SB_API size_t sb_spmv_csr_scratch_bytes(int64_t segments);
+SB_API size_t sb_spmv_csr_scratch_bytes(int64_t nnz);
 SB_API int sb_spmv_csr_f32(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
                            const int32_t* crd, const float* val, const float* x, float* y,
-                           const void* plan, int64_t plan_segments, void* scratch,
-                           size_t scratch_bytes, void* stream);
+                           void* scratch, size_t scratch_bytes, void* stream);
 SB_API int sb_spmv_csr_typed(int dtype, int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
                              const int32_t* crd, const void* val, const void* x, void* y,
                              void* stream);
@@ -128,16 +129,16 @@ SB_API int sb_spmv_csr_typed(int dtype, int64_t m, int64_t n, int64_t nnz, const
 /* SpMV that allocates nothing and asks the caller for no workspace.  (No counterpart in the
  * reference: its kernels malloc freely on the host.)  For callers that cannot call cudaMalloc —
  * a plugin living inside another runtime's device-memory arena, or a service that must not touch
- * the allocator after start-up.  Same result as sb_spmv_csr_f32; the row plan and the segment
- * scratch live in an array of SB_STATIC_SCRATCH_BYTES that is part of the library image, so each
- * GPU that loads the library holds that much memory until the process exits.
+ * the allocator after start-up.  Same result as sb_spmv_csr_f32; the scratch for the partial sums
+ * lives in an array of SB_STATIC_SCRATCH_BYTES that is part of the library image, so each GPU
+ * that loads the library holds that much memory until the process exits.
  *   - nnz above SB_STATIC_SPMV_MAX_NNZ is rejected with SB_ERR_UNSUPPORTED.
  *   - The first call on a device resolves the array's device address; make that call outside of
  *     any stream capture.
  *   - All calls share the array: calls that overlap on one GPU (other streams, other threads)
  *     race.  Serialise them, or use sb_spmv_csr_f32 with buffers of your own. */
 #define SB_STATIC_SPMV_MAX_NNZ (1LL << 26)
-#define SB_STATIC_SCRATCH_BYTES (2 << 20)
+#define SB_STATIC_SCRATCH_BYTES (512 << 10)
 SB_API int sb_spmv_csr_f32_static(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
                                   const int32_t* crd, const float* val, const float* x, float* y,
                                   void* stream);

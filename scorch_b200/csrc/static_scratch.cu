@@ -3,9 +3,9 @@
 // Some hosts of this library never get to call cudaMalloc: a plugin that runs inside another
 // runtime's memory budget (every byte on the device belongs to the host application's arena),
 // or a real-time / pre-initialised service that must not touch the allocator after start-up.
-// sb_spmv_csr_f32 needs two caller-provided buffers besides its inputs and outputs: the row plan
-// and the heavy-segment scratch.  The entry point below keeps both in one array that is part of
-// the library image, so the caller passes nothing but the matrix, x and y.
+// sb_spmv_csr_f32 needs one caller-provided buffer besides its inputs and outputs: the scratch
+// for the partial sums of rows cut by tile borders.  The entry point below keeps it in an array
+// that is part of the library image, so the caller passes nothing but the matrix, x and y.
 //
 // Price: every GPU that loads the library holds SB_STATIC_SCRATCH_BYTES of device memory until
 // the process exits, the supported nnz is capped, and because all calls share the one array,
@@ -16,13 +16,11 @@
 
 namespace sb {
 
-// plan for the largest supported matrix + one float per heavy segment
+// partial-sum arrays of the largest supported matrix: three 4-byte arrays with one slot per
+// 2048-entry tile (the layout of sb_spmv_csr_scratch_bytes)
 constexpr long long kStaticMaxNnz = SB_STATIC_SPMV_MAX_NNZ;
-constexpr long long kCapHeavy = kStaticMaxNnz / SB_HEAVY_ROW_NNZ + 1;
-constexpr long long kCapSeg = kStaticMaxNnz / SB_HEAVY_ROW_NNZ + kCapHeavy;
-constexpr long long kPlanBytes = ((8 + 3 * kCapHeavy + kCapSeg) * 4 + 255) / 256 * 256;
-constexpr long long kSegBytes = (kCapSeg * 4 + 255) / 256 * 256;
-static_assert(kPlanBytes + kSegBytes <= SB_STATIC_SCRATCH_BYTES, "static scratch too small");
+static_assert(((kStaticMaxNnz / 2048 + 1) * 4 + 255) / 256 * 256 * 3 <= SB_STATIC_SCRATCH_BYTES,
+              "static scratch too small");
 
 // In host code this name is only a handle for the symbol, not a device address: the address a
 // kernel can use comes from cudaGetSymbolAddress (below), once per device.
@@ -67,15 +65,9 @@ int sb_spmv_csr_f32_static(int64_t m, int64_t n, int64_t nnz, const int32_t* pos
   unsigned char* base = nullptr;
   int rc = static_scratch_ptr(&base);
   if (rc != SB_OK) return rc;
-  void* plan = base;
-  void* seg = base + kPlanBytes;
-  // The array keeps whatever the previous call left.  plan_build zeroes the plan header it
-  // counts into; every segment sum is written before the finalise kernel reads it.
-  rc = sb_csr_plan_build(m, nnz, pos, plan, (size_t)kPlanBytes, stream);
-  if (rc != SB_OK) return rc;
-  // -1: launch for the worst-case segment count of this nnz, so no count has to come back to
-  // the host (no synchronisation, no allocation); surplus CTAs exit at once.
-  return sb_spmv_csr_f32(m, n, nnz, pos, crd, val, x, y, plan, -1, seg, (size_t)kSegBytes, stream);
+  // The array keeps whatever the previous call left: every slot the fix-up kernel reads is
+  // written by the tile kernel of the same call first.
+  return sb_spmv_csr_f32(m, n, nnz, pos, crd, val, x, y, base, (size_t)SB_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

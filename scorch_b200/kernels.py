@@ -201,6 +201,8 @@ def _spmm_typed(pos, crd, val, B, n):
 
 
 def spmv_csr(pos, crd, val, x, plan: Optional[CsrPlan] = None) -> torch.Tensor:
+    """y = A @ x for CSR A (``plan`` is accepted for symmetry with ``spmm_csr`` and not needed:
+    the fp32 kernel is balanced by entries, not rows)."""
     pos = _dev(pos, torch.int32, "pos")
     crd = _dev(crd, torch.int32, "crd")
     m, nnz = pos.numel() - 1, crd.numel()
@@ -216,13 +218,10 @@ def spmv_csr(pos, crd, val, x, plan: Optional[CsrPlan] = None) -> torch.Tensor:
             check(L.sb_spmv_csr_typed(code, m, x.numel(), nnz, pos.data_ptr(), crd.data_ptr(),
                                       val.data_ptr(), x.data_ptr(), y.data_ptr(), _stream()))
             return y
-        if plan is None:
-            plan = plan_for(pos, nnz)
-        sbytes = L.sb_spmv_csr_scratch_bytes(plan.segments)
-        scratch = plan.scratch(sbytes) if sbytes else None
+        sbytes = L.sb_spmv_csr_scratch_bytes(nnz)
+        scratch = torch.empty(max(sbytes, 16), dtype=torch.uint8, device=x.device)
         check(L.sb_spmv_csr_f32(m, x.numel(), nnz, pos.data_ptr(), crd.data_ptr(), val.data_ptr(),
-                                x.data_ptr(), y.data_ptr(), plan.buf.data_ptr(), plan.segments,
-                                _ptr(scratch), sbytes, _stream()))
+                                x.data_ptr(), y.data_ptr(), scratch.data_ptr(), sbytes, _stream()))
     return y
 
 

@@ -37,7 +37,8 @@ def test_size_queries_are_pure_host_functions(sb_lib):
     assert sb_lib.sb_csr_plan_max_segments(nnz) >= 10
     assert sb_lib.sb_spmm_csr_scratch_bytes(7, 64, 2) == 7 * 64 * 2 * 4
     assert sb_lib.sb_spmm_csr_scratch_bytes(0, 64, 1) == 0
-    assert sb_lib.sb_spmv_csr_scratch_bytes(5) == 20
+    assert sb_lib.sb_spmv_csr_scratch_bytes(0) == 0
+    assert sb_lib.sb_spmv_csr_scratch_bytes(5000) == 3 * 256  # 3 tiles -> three padded arrays
     small = sb_lib.sb_spgemm_workspace_bytes(100, 100, 0)
     big = sb_lib.sb_spgemm_workspace_bytes(100, 1 << 20, 0)
     assert 0 < small < big
