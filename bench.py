@@ -428,8 +428,8 @@ class GcnSharded:
         self.max_row = int((g.pos[1:] - g.pos[:-1]).max().item())
         r0, r1 = self.shard.bounds[rank], self.shard.bounds[rank + 1]
         if rank == 0:
-            self.sample = (g.pos[:100_001].cpu(), g.crd[:int(g.pos[100_000])].cpu(),
-                           g.val[:int(g.pos[100_000])].cpu())
+            ns = min(100_000, self.n)
+            self.sample = (g.pos[:ns + 1].cpu(), g.crd[:int(g.pos[ns])].cpu(), g.val[:int(g.pos[ns])].cpu())
         del g
         torch.cuda.empty_cache()
         gen = torch.Generator(device="cuda").manual_seed(1)
@@ -503,7 +503,7 @@ class GcnSharded:
         from oracle import oracle as O, ref_loader
         ref = ref_loader.load()
         pos, crd, val = self.sample
-        rows, n, k = 100_000, self.n, 256
+        rows, n, k = pos.numel() - 1, self.n, 256
         B = torch.randn((n, k), dtype=torch.float32)
         t0 = time.perf_counter()
         if ref is not None:
@@ -516,9 +516,9 @@ class GcnSharded:
                                                            f"({crd.numel()} entries), spmm_csr_float_v2 ({kind})")
 
 
-def make_workload(name: str, world: int = 1):
+def make_workload(name: str, world: int = 1, c4_nodes: int = 2_000_000):
     if name == "c4":
-        return GcnSharded(world=world)
+        return GcnSharded(n=c4_nodes, world=world)
     if name == "c2":
         return SparseAttention()
     if name in ("c1", "c3"):
@@ -532,7 +532,7 @@ def make_workload(name: str, world: int = 1):
 def run_reference(args, rank: int, emit):
     if rank != 0:
         return
-    wl = make_workload(args.workload)
+    wl = make_workload(args.workload, 1, args.c4_nodes)
     if args.workload == "c2":
         # build host inputs only (no CUDA needed for this arm)
         from scorch_b200 import workloads as W
@@ -577,6 +577,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-units", type=int, default=2, help="heads in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--c4-nodes", type=int, default=2_000_000,
+                    help="graph size of workload c4 (smaller graphs are for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -616,7 +618,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    wl = make_workload(args.workload, world)
+    wl = make_workload(args.workload, world, args.c4_nodes)
     wl.setup(rank)
     K, W_ = args.steps, args.warmup
 
