@@ -42,7 +42,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes (read + write) per launch of each kernel from ncu captures of this benchmark's
 # default workload, summarised under profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {                        # profiles/c2_sparse_attention_kernels.md
+NCU_TRAFFIC_BYTES = {                        # from the ncu capture summarised under profiles/
     "sddmm_kernel": 273_008_640,             # SDDMM stage: block kernel + remainder kernel
     "csr_row_softmax_kernel": 251_335_936,
     "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel

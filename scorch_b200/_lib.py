@@ -8,7 +8,9 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libscorch_b200.so")
+# SCORCH_B200_LIB points at another build of the same library (e.g. one compiled with different
+# tuning macros); by default the in-tree build is loaded.
+LIB_PATH = os.environ.get("SCORCH_B200_LIB") or os.path.join(_HERE, "libscorch_b200.so")
 
 SB_OK = 0
 SB_F32, SB_F64, SB_I32, SB_I64 = 0, 1, 2, 3

@@ -204,14 +204,17 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
     H = shard.buffer("hidden", (rows, k1), dev)
     out = torch.empty((rows, k2), dtype=torch.float32, device=dev)
 
-    pending = []
-    for i, (c, w) in enumerate(p1):
+    send2 = [shard.buffer(f"l2send{j}", (shard.max_rows, w), dev) for j, (_, w) in enumerate(p2)]
+    pending, pending2 = [], []
+
+    def produce(i):   # layer-1 transform of panel i and its gather
+        c, w = p1[i]
         send = shard.buffer(f"l1send{i}", (shard.max_rows, w), dev)
         torch.matmul(x_local, W1[:, c:c + w], out=send[:rows])
         pending.append(g.gather(f"l1recv{i}", send))
-    send2 = [shard.buffer(f"l2send{j}", (shard.max_rows, w), dev) for j, (_, w) in enumerate(p2)]
-    pending2 = []
-    for i, (c, w) in enumerate(p1):
+
+    def consume(i):   # SpMM of panel i, then its contribution to layer 2's operands
+        c, w = p1[i]
         buf, ev = pending[i]
         g.wait(ev)
         hp = H[:, c:c + w]
@@ -225,6 +228,16 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
                 dst.addmm_(hp, W2[c:c + w, c2:c2 + w2])
             if last:
                 pending2.append(g.gather(f"l2recv{j}", send2[j]))
+
+    # transforms run `lookahead` panels ahead of the SpMMs on the main stream: the first SpMM is
+    # issued when its gather is about to land instead of behind every transform
+    lookahead = 2
+    for i in range(len(p1)):
+        produce(i)
+        if i >= lookahead:
+            consume(i - lookahead)
+    for i in range(max(0, len(p1) - lookahead), len(p1)):
+        consume(i)
     for j, (c2, w2) in enumerate(p2):
         buf, ev = pending2[j]
         g.wait(ev)

@@ -1,7 +1,7 @@
 """Generate the golden vectors in this directory by running the REFERENCE itself.
 
-Run in a container that has the reference checkout (default /root/reference) and the compiled
-reference extension (``python oracle/build_ref.py``):
+Run in a container that has the reference checkout (its location: SCORCH_REFERENCE_ROOT, see the
+default below) and the compiled reference extension (``python oracle/build_ref.py``):
 
     python tests/golden/make_golden.py
 
