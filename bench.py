@@ -567,11 +567,27 @@ def run_reference(args, rank: int, emit):
     emit(line)
 
 
+def _bind_to_gpu_numa_node(index: int) -> None:
+    """Run this rank (and allocate its pinned buffers) on the CPUs that sit next to its GPU: with
+    one process per GPU the host-to-device copies of the end-to-end arm otherwise cross sockets."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:
+        pass
+
+
 # ---- main -------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -602,6 +618,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); "
                          "use --impl reference for the CPU arm")
     torch.cuda.set_device(local_rank)
+    _bind_to_gpu_numa_node(local_rank)
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
