@@ -42,10 +42,17 @@ FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes (read + write) per launch of each kernel from ncu captures of this benchmark's
 # default workload, summarised under profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {                        # from the ncu capture summarised under profiles/
-    "sddmm_kernel": 273_008_640,             # SDDMM stage: block kernel + remainder kernel
-    "csr_row_softmax_kernel": 251_335_936,
-    "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel
+NCU_TRAFFIC_BYTES = {
+    "three operators": {
+        "sddmm_kernel": 273_008_640,             # SDDMM stage: block kernel + remainder kernel
+        "csr_row_softmax_kernel": 251_335_936,
+        "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel
+    },
+    "one attention call": {
+        "sddmm_kernel": None,
+        "attn_block_kernel": None,
+        "spmm_rows_kernel": None,
+    },
 }
 
 
@@ -135,8 +142,16 @@ class SparseAttention:
         self.nnz = self.mask.nnz
         self.plan = K.CsrPlan(self.pos, self.nnz)
         from scorch_b200 import pipelines as P
-        self.block_plan = None if os.environ.get("SCORCH_B200_NO_BLOCKS") else P.attention_block_plan(self.pos, self.crd)
-        self.scores = torch.empty((self.units, self.nnz), dtype=torch.float32, device="cuda")
+        no_blocks = bool(os.environ.get("SCORCH_B200_NO_BLOCKS"))
+        # the one-call attention path (what pipelines.sparse_attention picks for this mask); the
+        # three-operator path is timed instead with SCORCH_B200_NO_FUSED=1
+        self.attn_plan = (None if no_blocks or os.environ.get("SCORCH_B200_NO_FUSED")
+                          else P.attention_plan(self.pos, self.crd, self.d, self.d))
+        self.block_plan = None if no_blocks or self.attn_plan else P.attention_block_plan(self.pos, self.crd)
+        if self.attn_plan:
+            self.kernels = ("sddmm_kernel", "attn_block_kernel", "spmm_rows_kernel")
+        self.scores = (None if self.attn_plan else
+                       torch.empty((self.units, self.nnz), dtype=torch.float32, device="cuda"))
         self.out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, device="cuda")
         from scorch_b200 import pipelines as P
         self.host_api = P.HostSparseAttention(self.pos, self.crd, self.mval, self.units, self.seq, self.d)
@@ -146,17 +161,34 @@ class SparseAttention:
         return 2 * (2.0 * self.nnz * self.d) * self.units
 
     def config(self):
+        bp = self.attn_plan or self.block_plan
+        scores = 0 if self.attn_plan else self.units * self.nnz * 4
         return {"workload": self.name, "units_per_gpu": self.units, "seq": self.seq, "head_dim": self.d,
                 "mask_nnz": self.nnz,
-                "dense_16x16_blocks": self.block_plan.blocks if self.block_plan else 0,
-                "entries_outside_blocks": self.block_plan.rem_nnz if self.block_plan else self.nnz,
-                "l2": "inputs larger than L2 (Q,K,V,scores,mask = "
-                f"{(3 * self.units * self.seq * self.d * 4 + self.units * self.nnz * 4 + self.nnz * 8) >> 20} MiB)"}
+                "path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
+                         if self.attn_plan else "sddmm, row softmax, spmm"),
+                "blocks_16x16": bp.blocks if bp else 0,
+                "entries_outside_blocks": bp.rem_nnz if bp else self.nnz,
+                "l2": "inputs larger than L2 (Q,K,V,O,scores,mask = "
+                f"{(4 * self.units * self.seq * self.d * 4 + scores + self.nnz * 8) >> 20} MiB)"}
 
     def alg_bytes(self):
         """Algorithmic bytes per launch (each array read once / written once)."""
         nnz, s, d, u = self.nnz, self.seq, self.d, self.units
         idx = (s + 1) * 4 + nnz * 4
+        if self.attn_plan:
+            rem, blocks = self.attn_plan.rem_nnz, self.attn_plan.blocks
+            rem_idx = (s + 1) * 4 + 2 * rem * 4          # rem_pos, rem_ent, crd of the listed entries
+            return {
+                # scores of the remaining entries: index lists, mask values, Q and K in, scores out
+                "sddmm_kernel": rem_idx + rem * 4 + u * (2 * s * d * 4 + rem * 4),
+                # blocks: plan (column, first entry and mask per block row), mask values of the block
+                # entries, Q, K, V in, O out, remaining scores in / probabilities out
+                "attn_block_kernel": blocks * (4 + 64 + 64) + (nnz - rem) * 4
+                                     + u * (4 * s * d * 4 + 2 * rem * 4),
+                # P V of the remaining entries: index lists, probabilities and V in, O in and out
+                "spmm_rows_kernel": rem_idx + u * (rem * 4 + 3 * s * d * 4),
+            }
         return {
             "sddmm_kernel": idx + nnz * 4 + u * (2 * s * d * 4 + nnz * 4),
             "csr_row_softmax_kernel": (s + 1) * 4 + u * (2 * nnz * 4),
@@ -167,6 +199,15 @@ class SparseAttention:
         K = self.K
         if ev is not None:
             ev[0].record()
+        if self.attn_plan:
+            # the attention call, kernel by kernel so that each can be timed (stages 1, 2, 4 of
+            # kernels.sparse_attention_csr; together they are the default stages=7 call)
+            for j, stage in enumerate((1, 2, 4)):
+                K.sparse_attention_csr(self.pos, self.crd, self.mval, Q, Km, V, attn_plan=self.attn_plan,
+                                       out=self.out, stages=stage)
+                if ev is not None:
+                    ev[j + 1].record()
+            return
         # same calls as pipelines.sparse_attention, with preallocated outputs
         s = K.sddmm_csr(self.pos, self.crd, self.mval, Q, Km, out=self.scores, block_plan=self.block_plan)
         if ev is not None:
@@ -184,7 +225,7 @@ class SparseAttention:
 
     @property
     def launches_per_step(self):
-        return 5 if self.block_plan else 3
+        return 5 if self.block_plan else 3   # (the attention call: 3 kernels)
 
     def step(self, ev=None):
         self._run(self.Q, self.Km, self.V, ev)
@@ -699,7 +740,8 @@ def main():
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "algorithmic_bytes_per_launch": alg[dom],
                 "launch_ms": stage_ms[dom],
-                "traffic": NCU_TRAFFIC_BYTES.get(dom) if args.workload == "c2" else None,
+                "traffic": (NCU_TRAFFIC_BYTES["one attention call" if wl.attn_plan else "three operators"].get(dom)
+                            if args.workload == "c2" else None),
                 "per_kernel": {k: {"ms": stage_ms[k], "algorithmic_GBps": (alg[k] / (stage_ms[k] * 1e-3) / 1e9)
                                    if stage_ms[k] else None} for k in stage_ms}}
 

@@ -50,6 +50,13 @@ SIGNATURES = {
     "sb_spmm_csr_blocked_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                        _int, _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _i64,
                                        _ptr]),
+    "sb_attn_plan_bytes": (_sz, [_i64, _i64]),
+    "sb_attn_plan_build": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _sz, C.POINTER(_i64),
+                                  C.POINTER(_i64), _ptr]),
+    "sb_sparse_attention_scratch_bytes": (_sz, [_i64, _i64]),
+    "sb_sparse_attention_csr_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
+                                           _i64, _ptr, _i64, _f32, _ptr, _i64, _i64, _i64, _i64, _i64,
+                                           _i64, _ptr, _i64, _i64, _ptr, _sz, _int, _ptr]),
     "sb_csr_row_softmax_f32": (_int, [_i64, _i64, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr]),
     "sb_spgemm_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "sb_spgemm_symbolic": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr,

@@ -15,6 +15,7 @@
 // rtol 1e-4 contract).  Tiles are 16x16, far below the 64/128-row minimum of the tcgen05 path,
 // so the warp-level mma is the fitting instruction here.
 #include "common.cuh"
+#include "mma_tf32.cuh"
 
 namespace sb {
 
@@ -156,31 +157,6 @@ rem_fill_kernel(int m, const int* __restrict__ pos, const int* __restrict__ crd,
     if (keep) rem_ent[outp + __popc(mask & ((1u << lane) - 1))] = p;
     outp += __popc(mask);
   }
-}
-
-// ---- 3xTF32 tensor-core helpers ---------------------------------------------------------------------
-__device__ __forceinline__ void split_tf32(float x, unsigned& hi, unsigned& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-  const float r = x - __uint_as_float(hi);
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
-}
-
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const unsigned (&a)[4], unsigned b0,
-                                         unsigned b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// c += a * b with fp32-level accuracy: small cross terms first, then the main term.
-__device__ __forceinline__ void mma_3xtf32(float (&c)[4], const unsigned (&ahi)[4],
-                                           const unsigned (&alo)[4], unsigned bhi0, unsigned bhi1,
-                                           unsigned blo0, unsigned blo1) {
-  mma_tf32(c, alo, bhi0, bhi1);
-  mma_tf32(c, ahi, blo0, blo1);
-  mma_tf32(c, ahi, bhi0, bhi1);
 }
 
 struct BlockArgs {
@@ -377,16 +353,6 @@ spmm_block_kernel(BlockArgs a, const float* __restrict__ val, const float* __res
   }
 }
 
-// entry points of the remainder kernels (sddmm.cu / spmm.cu)
-int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, const int* rem_ent,
-                    const int* crd, const float* mask_val, const float* Q, int64_t ldq,
-                    const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,
-                    int64_t stride_k, int64_t stride_out, cudaStream_t st);
-int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent, const int* crd,
-                   const float* val, const float* B, int64_t ldb, const float* bias, int relu,
-                   float* C, int64_t ldc, int64_t batch, int64_t stride_val, int64_t stride_b,
-                   int64_t stride_c, cudaStream_t st);
-
 }  // namespace sb
 
 using namespace sb;
@@ -475,7 +441,7 @@ int sb_sddmm_csr_blocked_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const
   }
   if (rem_nnz > 0)
     return sddmm_remainder(m, d, rem_nnz, p.rem_pos, p.rem_ent, crd, mask_val, Q, ldq, K, ldk, out_val,
-                           batch, stride_q, stride_k, stride_out, st);
+                           batch, stride_q, stride_k, stride_out, 0, st);
   return SB_OK;
 }
 
@@ -509,7 +475,7 @@ int sb_spmm_csr_blocked_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const 
   SB_LAUNCH_CHECK("spmm_block_kernel");
   // the remainder kernel adds its rows to C and applies bias / ReLU (also when rem_nnz == 0)
   return spmm_remainder(m, k, p.rem_pos, p.rem_ent, crd, val, B, ldb, bias, relu, C, ldc, batch,
-                        stride_val, stride_b, stride_c, st);
+                        stride_val, stride_b, stride_c, 0, st);
 }
 
 }  // extern "C"

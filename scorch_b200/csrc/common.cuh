@@ -66,6 +66,19 @@ PlanView plan_view(const void* plan, int64_t nnz);
 int exclusive_scan_i32(int n, const int* cnt, int* out, long long* block_sum, long long* total_dev,
                        cudaStream_t st);
 
+// Gather kernels over the entries that a block plan leaves outside its blocks (sddmm.cu /
+// spmm.cu): entries are taken through the list `rem_ent`, rows described by `rem_pos`.
+// out_compact / val_compact: results / values are indexed by position in the list instead of by
+// entry of the original pattern.
+int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, const int* rem_ent,
+                    const int* crd, const float* mask_val, const float* Q, int64_t ldq,
+                    const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,
+                    int64_t stride_k, int64_t stride_out, int out_compact, cudaStream_t st);
+int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent, const int* crd,
+                   const float* val, const float* B, int64_t ldb, const float* bias, int relu,
+                   float* C, int64_t ldc, int64_t batch, int64_t stride_val, int64_t stride_b,
+                   int64_t stride_c, int val_compact, cudaStream_t st);
+
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__
 

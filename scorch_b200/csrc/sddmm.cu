@@ -32,6 +32,7 @@ struct SddmmArgs {
   int rowwise;            // one warp per row of pos[] (short rows) instead of one per entry span
   const int* ent;         // optional entry list: entry q of this launch is entry ent[q] of crd /
                           // mask_val / out_val (pos then describes the listed entries per row)
+  int out_compact;        // with ent: result of listed entry q goes to out_val[q], not out_val[ent[q]]
   const float* mask_val;  // may be null
   const float* Q;
   long long ldq;
@@ -221,7 +222,7 @@ sddmm_kernel(SddmmArgs a) {
       }
     }
     transpose_reduce<G>(part, lane);
-    if (lane < cnt) out[my_p] = my_s * part[0];
+    if (lane < cnt) out[a.out_compact ? p0 + lane : my_p] = my_s * part[0];
   }
 }
 
@@ -343,8 +344,8 @@ static int check_sddmm(int64_t m, int64_t n, int64_t d, int64_t nnz, const void*
 int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, const int* rem_ent,
                     const int* crd, const float* mask_val, const float* Q, int64_t ldq,
                     const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,
-                    int64_t stride_k, int64_t stride_out, cudaStream_t st) {
-  SddmmArgs a{(int)m, (int)d, rem_nnz, rem_pos, nullptr, crd, 1, rem_ent, mask_val, Q, ldq, K, ldk, out,
+                    int64_t stride_k, int64_t stride_out, int out_compact, cudaStream_t st) {
+  SddmmArgs a{(int)m, (int)d, rem_nnz, rem_pos, nullptr, crd, 1, rem_ent, out_compact, mask_val, Q, ldq, K, ldk, out,
               nullptr, nullptr, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, st);
 }
@@ -363,7 +364,7 @@ int sb_sddmm_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, crd, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(pos, "sddmm_csr: pos is null");
-  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, 0, nullptr, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, pos, nullptr, crd, 0, nullptr, 0, mask_val, Q, ldq, K, ldk, out_val,
               out_row, out_col, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }
@@ -375,7 +376,7 @@ int sb_sddmm_coo_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t
   int rc = check_sddmm(m, n, d, nnz, col, Q, ldq, K, ldk, out_val, batch);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(nnz == 0 || row, "sddmm_coo: row is null");
-  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, 0, nullptr, mask_val, Q, ldq, K, ldk, out_val,
+  SddmmArgs a{(int)m, (int)d, nnz, nullptr, row, col, 0, nullptr, 0, mask_val, Q, ldq, K, ldk, out_val,
               nullptr, nullptr, stride_q, stride_k, stride_out};
   return sddmm_dispatch(a, batch, (cudaStream_t)stream);
 }

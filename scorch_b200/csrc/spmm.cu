@@ -38,6 +38,7 @@ struct SpmmArgs {
   long long stride_val, stride_b, stride_c;
   int skip_heavy;  // rows longer than SB_HEAVY_ROW_NNZ are left to the heavy kernels
   const int* ent;  // optional entry list: entry p of pos[] is entry ent[p] of crd / val
+  int val_compact; // with ent: the value of listed entry p is val[p], not val[ent[p]]
   int accumulate;  // add to the existing contents of C (before bias / ReLU)
 };
 
@@ -87,7 +88,8 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
                                                  const float* __restrict__ val,
                                                  const float* __restrict__ Bcol, unsigned ldb,
                                                  int b, int e, int lane, const bool (&col_ok)[VEC],
-                                                 const int* __restrict__ ent = nullptr) {
+                                                 const int* __restrict__ ent = nullptr,
+                                                 bool val_compact = false) {
   constexpr int G = 32 / L;
   const int g = lane / L;
   // software pipeline: the next chunk's indices/values are in flight while this chunk's rows of
@@ -97,7 +99,7 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
   if (b + lane < e) {
     const int x = ent ? ld_stream(ent + b + lane) : b + lane;
     next_j = ld_stream(crd + x);
-    next_a = ld_stream(val + x);
+    next_a = ld_stream(val + (val_compact ? b + lane : x));
   }
   for (int p0 = b; p0 < e; p0 += 32) {
     const int cnt = min(32, e - p0);
@@ -106,7 +108,7 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
     if (p0 + 32 + lane < e) {
       const int x = ent ? ld_stream(ent + p0 + 32 + lane) : p0 + 32 + lane;
       next_j = ld_stream(crd + x);
-      next_a = ld_stream(val + x);
+      next_a = ld_stream(val + (val_compact ? p0 + 32 + lane : x));
     }
     if (cnt == 32) {
       constexpr int STEPS = 32 / G;
@@ -213,7 +215,7 @@ spmm_rows_kernel(SpmmArgs a) {
   }
   accumulate_range<L, VEC, W, EXACT>(acc, a.crd, a.val + bz * a.stride_val,
                                            a.B + bz * a.stride_b + col0, (unsigned)a.ldb, b, e,
-                                           lane, col_ok, a.ent);
+                                           lane, col_ok, a.ent, a.val_compact != 0);
   reduce_groups<L, VEC, W>(acc);
   if (lane < L) {
     float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
@@ -434,12 +436,12 @@ static int spmm_vec_dispatch(const SpmmArgs& a, int64_t k, int64_t ldb, int64_t 
 int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent, const int* crd,
                    const float* val, const float* B, int64_t ldb, const float* bias, int relu,
                    float* C, int64_t ldc, int64_t batch, int64_t stride_val, int64_t stride_b,
-                   int64_t stride_c, cudaStream_t st) {
+                   int64_t stride_c, int val_compact, cudaStream_t st) {
   SpmmArgs a;
   a.m = (int)m; a.k = (int)k; a.pos = rem_pos; a.crd = crd; a.val = val; a.B = B; a.ldb = ldb;
   a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
   a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
-  a.skip_heavy = 0; a.ent = rem_ent; a.accumulate = 1;
+  a.skip_heavy = 0; a.ent = rem_ent; a.val_compact = val_compact; a.accumulate = 1;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, nullptr, 0, 0, nullptr, st);
 }
 
@@ -505,6 +507,7 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
   a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
   a.skip_heavy = (plan && plan_segments != 0) ? 1 : 0;
   a.ent = nullptr;
+  a.val_compact = 0;
   a.accumulate = 0;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, plan, nnz, plan_segments, scratch, st);
 }

@@ -102,6 +102,94 @@ def block_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> BlockPlan:
     return plan
 
 
+class AttnPlan:
+    """Blocks (aligned 16x16, at least 64 stored entries, with per-row column masks) + remaining
+    entries of one CSR attention mask; see include/scorch_b200.h.  ``block_fraction`` is the share
+    of the stored entries that lie in blocks."""
+
+    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, n: Optional[int] = None):
+        pos, crd = _dev(pos, torch.int32, "pos"), _dev(crd, torch.int32, "crd")
+        self.m, self.nnz = pos.numel() - 1, crd.numel()
+        self.n = self.m if n is None else n
+        L = _lib.lib()
+        nbytes = L.sb_attn_plan_bytes(self.m, self.nnz)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=pos.device)
+        b, r = C.c_int64(0), C.c_int64(0)
+        with torch.cuda.device(pos.device):
+            check(L.sb_attn_plan_build(self.m, self.n, self.nnz, pos.data_ptr(), crd.data_ptr(),
+                                       self.buf.data_ptr(), nbytes, C.byref(b), C.byref(r), _stream()))
+        self.blocks, self.rem_nnz = int(b.value), int(r.value)
+        self._scratch: Optional[torch.Tensor] = None
+
+    @property
+    def block_fraction(self) -> float:
+        return (self.nnz - self.rem_nnz) / self.nnz if self.nnz else 0.0
+
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.buf.device)
+        return self._scratch
+
+
+def attn_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> AttnPlan:
+    """Attention plan of a square mask, cached on the ``crd`` tensor object (rebuilt after
+    in-place writes)."""
+    cached = getattr(crd, "_sb_attn_plan", None)
+    if cached is not None and cached[0] == (pos._version, crd._version, pos.data_ptr()):
+        return cached[1]
+    plan = AttnPlan(pos, crd)
+    crd._sb_attn_plan = ((pos._version, crd._version, pos.data_ptr()), plan)
+    return plan
+
+
+FUSED_ATTENTION_D = (32, 64)
+
+
+def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
+                         attn_plan: Optional[AttnPlan] = None,
+                         out: Optional[torch.Tensor] = None, stages: int = 7) -> torch.Tensor:
+    """O = softmax_rows(scale * mask_val .* (Q Kmat^T) on the stored entries) V in one call, the
+    scores never written out.  Q: (m, d) or (batch, m, d); Kmat, V: (n, d) or (batch, n, d); head
+    dimension d in FUSED_ATTENTION_D.  Rows without stored entries give zero rows.
+    ``stages``: 7 = the whole call; 1, 2, 4 = its three kernels one by one (in that order, same
+    arguments), for callers that time them."""
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    m, nnz = pos.numel() - 1, crd.numel()
+    Q, Kmat, V = (_dev(x, torch.float32, nm).contiguous() for x, nm in ((Q, "Q"), (Kmat, "K"), (V, "V")))
+    batched = Q.dim() == 3
+    batch = Q.shape[0] if batched else 1
+    d, n = Q.shape[-1], Kmat.shape[-2]
+    if d not in FUSED_ATTENTION_D:
+        raise ValueError(f"head dimension must be one of {FUSED_ATTENTION_D}")
+    if Q.shape[-2] != m or Kmat.shape != V.shape or Kmat.shape[-1] != d or Kmat.dim() != Q.dim() \
+            or (batched and Kmat.shape[0] != batch):
+        raise ValueError("Q must be (.., m, d) and K, V (.., n, d) with the same batch")
+    if mask_val is not None:
+        mask_val = _dev(mask_val, torch.float32, "mask_val")
+        if mask_val.numel() != nnz:
+            raise ValueError("mask_val and crd differ in length")
+    if attn_plan is None:
+        attn_plan = AttnPlan(pos, crd, n=n) if n != m else attn_plan_for(pos, crd)
+    if attn_plan.m != m or attn_plan.nnz != nnz or attn_plan.n != n:
+        raise ValueError("attention plan was built for another mask")
+    shape = (batch, m, d) if batched else (m, d)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=Q.device)
+    elif not (out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == shape and out.is_contiguous()):
+        raise ValueError(f"out must be a contiguous float32 CUDA tensor of shape {shape}")
+    L = _lib.lib()
+    sbytes = L.sb_sparse_attention_scratch_bytes(attn_plan.rem_nnz, batch)
+    scratch = attn_plan.scratch(sbytes) if sbytes else None
+    with torch.cuda.device(Q.device):
+        check(L.sb_sparse_attention_csr_f32(m, n, d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val),
+                                            Q.data_ptr(), d, Kmat.data_ptr(), d, V.data_ptr(), d,
+                                            float(scale), out.data_ptr(), d, batch, m * d, n * d, n * d,
+                                            m * d, attn_plan.buf.data_ptr(), attn_plan.blocks,
+                                            attn_plan.rem_nnz, _ptr(scratch), sbytes, int(stages), _stream()))
+    return out
+
+
 BLOCKED_MIN_DENSE_FRACTION = 0.5   # below this the gather kernels alone are used
 _BLOCKED_SDDMM_D = (16, 32, 64, 128)
 _BLOCKED_SPMM_K = (32, 64, 128)

@@ -4,7 +4,8 @@ on the device end to end.
 * ``sparse_attention`` — per (batch, head): S = SDDMM(mask, Q, K), row softmax over the stored
   entries, O = SpMM(S, V).  Reference caller: bench/bench_sparse_transformer.py:304-382, which
   loops over heads in Python and does the softmax with torch scatter ops; here all heads go
-  through one batched launch per stage.
+  through one batched launch per stage, or — for masks with enough well-filled 16x16 blocks and
+  head dimension 32 / 64 — through the single attention call that never writes the scores.
 * ``gcn_forward`` — H = ReLU(A_hat (X W1)), out = A_hat (H W2), transform first like the
   reference's bench (bench/bench_gcn.py:314-329).  The dense X·W products are cuBLAS calls
   through torch (outside the sparse path); the two A_hat products are the SpMM kernel, the first
@@ -26,13 +27,33 @@ def attention_block_plan(pos: torch.Tensor, crd: torch.Tensor) -> Optional[K.Blo
     return bp if bp.dense_fraction >= K.BLOCKED_MIN_DENSE_FRACTION else None
 
 
+def attention_plan(pos: torch.Tensor, crd: torch.Tensor, d: int, dv: int) -> Optional[K.AttnPlan]:
+    """The mask's attention plan if the one-call path applies: square mask, head dimension 32 / 64
+    for Q, K and V, and enough of the mask in well-filled 16x16 blocks; else None."""
+    if d != dv or d not in K.FUSED_ATTENTION_D:
+        return None
+    ap = K.attn_plan_for(pos, crd)
+    return ap if ap.block_fraction >= K.BLOCKED_MIN_DENSE_FRACTION else None
+
+
 def sparse_attention(pos: torch.Tensor, crd: torch.Tensor, mask_val: Optional[torch.Tensor],
                      Q: torch.Tensor, Kmat: torch.Tensor, V: torch.Tensor, scale: float = 1.0,
                      plan: Optional[K.CsrPlan] = None, scores_out: Optional[list] = None,
-                     block_plan="auto") -> torch.Tensor:
+                     block_plan="auto", fused="auto") -> torch.Tensor:
     """Q, K, V: (units, seq, d) with units = batch*heads.  Returns O (units, seq, d).
     ``block_plan``: "auto" (use the dense-block kernels when the mask has enough dense blocks),
-    None (gather kernels only) or a ``kernels.BlockPlan``."""
+    None (gather kernels only) or a ``kernels.BlockPlan``.
+    ``fused``: "auto" (one attention call when the mask and head dimension qualify, the scores
+    are not asked for and ``block_plan`` is "auto"), False (always the three operators) or a
+    ``kernels.AttnPlan``."""
+    if isinstance(fused, str):
+        fused = (attention_plan(pos, crd, Q.shape[-1], V.shape[-1])
+                 if scores_out is None and isinstance(block_plan, str) and Kmat.shape[-2] == Q.shape[-2]
+                 else None)
+    if fused:
+        if scores_out is not None:
+            raise ValueError("the one-call attention path does not produce the scores")
+        return K.sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale=scale, attn_plan=fused)
     if isinstance(block_plan, str):
         block_plan = attention_block_plan(pos, crd)
     s = K.sddmm_csr(pos, crd, mask_val, Q, Kmat, block_plan=block_plan)   # (units, nnz)
@@ -61,10 +82,12 @@ class HostSparseAttention:
         self.pos, self.crd, self.mask_val, self.scale = pos, crd, mask_val, scale
         self.units, self.seq, self.d = units, seq, d
         self.plan = K.plan_for(pos, crd.numel())
-        self.block_plan = attention_block_plan(pos, crd)
+        self.attn_plan = attention_plan(pos, crd, d, d)
+        self.block_plan = None if self.attn_plan else attention_block_plan(pos, crd)
         self.bounds = [units * c // chunks for c in range(chunks + 1)]
         self.dev = [torch.empty((units, seq, d), dtype=torch.float32, device=dev) for _ in range(3)]
-        self.scores = torch.empty((units, crd.numel()), dtype=torch.float32, device=dev)
+        self.scores = (None if self.attn_plan else
+                       torch.empty((units, crd.numel()), dtype=torch.float32, device=dev))
         self.out = torch.empty((units, seq, d), dtype=torch.float32, device=dev)
         self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
@@ -85,11 +108,16 @@ class HostSparseAttention:
                 arrived = torch.cuda.Event()
                 arrived.record(self.s_in)
             main.wait_event(arrived)
-            s = K.sddmm_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1], self.dev[1][u0:u1],
-                            out=self.scores[u0:u1], block_plan=self.block_plan)
-            K.csr_row_softmax(self.pos, s, scale=self.scale, out=s)
-            K.spmm_csr(self.pos, self.crd, s, self.dev[2][u0:u1], plan=self.plan, out=self.out[u0:u1],
-                       block_plan=self.block_plan)
+            if self.attn_plan:
+                K.sparse_attention_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1],
+                                       self.dev[1][u0:u1], self.dev[2][u0:u1], scale=self.scale,
+                                       attn_plan=self.attn_plan, out=self.out[u0:u1])
+            else:
+                s = K.sddmm_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1], self.dev[1][u0:u1],
+                                out=self.scores[u0:u1], block_plan=self.block_plan)
+                K.csr_row_softmax(self.pos, s, scale=self.scale, out=s)
+                K.spmm_csr(self.pos, self.crd, s, self.dev[2][u0:u1], plan=self.plan, out=self.out[u0:u1],
+                           block_plan=self.block_plan)
             computed = torch.cuda.Event()
             computed.record(main)
             with torch.cuda.stream(self.s_out):
