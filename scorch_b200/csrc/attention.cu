@@ -245,19 +245,13 @@ struct AttnArgs {
 //               the two products.  B of column tile u is V[8n+2t (+1)][g*KT + u] (logical column
 //               (u, g) = actual column g*KT + u), so a thread reads KT contiguous floats per V
 //               row and writes KT contiguous floats per output row.
-#ifndef ATTN_SPLIT
-#define ATTN_SPLIT 1   // 0: cvt.rna both parts; 1: truncate both parts; 2: truncate hi, raw fp32 bits as lo
-#endif
+// x = hi + lo with both parts valid TF32 values (low 13 mantissa bits zero): hi is x truncated,
+// lo the truncated remainder, so hi*hi + hi*lo + lo*hi misses the product by ~2^-20 relative.
+// (Two logic operations and one subtraction; rounding instead of truncating measured slower
+// and no more accurate at the fp32 level.)
 __device__ __forceinline__ void attn_split(float x, unsigned& hi, unsigned& lo) {
-#if ATTN_SPLIT == 0
-  split_tf32(x, hi, lo);
-#elif ATTN_SPLIT == 1
   hi = __float_as_uint(x) & 0xffffe000u;
   lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
-#else
-  hi = __float_as_uint(x) & 0xffffe000u;
-  lo = __float_as_uint(x - __uint_as_float(hi));
-#endif
 }
 // 256-bit read-only load (32-byte aligned): one instruction covers whole 128-byte lines of the
 // K / V rows, half the L1 wavefronts of 128-bit loads
@@ -270,20 +264,16 @@ __device__ __forceinline__ Float8 ldg8(const float* p) {
                : "l"(p));
   return r;
 }
-#ifndef ATTN_MINB
-#define ATTN_MINB 3
-#endif
-#ifndef ATTN_VEARLY
-#define ATTN_VEARLY 1
-#endif
+constexpr int kAttnWarps = 4;  // row blocks per CTA (1 and 2 measured the same)
 template <int D16>  // head dimension d = 16 * D16 (of Q, K and V)
-__global__ void __launch_bounds__(128, ATTN_MINB)
+// (three CTAs per SM: 168 registers; four spill, two leave the tensor pipe idle more often)
+__global__ void __launch_bounds__(kAttnWarps * 32, 12 / kAttnWarps)
 attn_block_kernel(AttnArgs a) {
   constexpr int KT = 2 * D16;
   // the warp's Q rows as pre-split TF32 A fragments, one 128-bit word per lane and k-step
-  __shared__ uint4 sq_hi[4][2 * D16][32], sq_lo[4][2 * D16][32];
+  __shared__ uint4 sq_hi[kAttnWarps][2 * D16][32], sq_lo[kAttnWarps][2 * D16][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rb = blockIdx.x * 4 + warp;
+  const int rb = blockIdx.x * kAttnWarps + warp;
   if (rb >= a.RB) return;
   const int g = lane >> 2, t = lane & 3;
   const long long bz = blockIdx.y;
@@ -298,8 +288,9 @@ attn_block_kernel(AttnArgs a) {
   const float* mask_val = (a.mask_val && !__ldg(a.mask_is_ones)) ? a.mask_val : nullptr;
 
   // running maximum M and (per-thread partial) sum L of both rows, started from the rows'
-  // remainder scores: lanes t = 0..3 of a row take every fourth entry
-  float M[2], L[2];
+  // remainder scores: the 4 lanes of a row take them in chunks of 32 (8 independent loads per
+  // lane and row), each lane keeping a running (max, sum) pair; the pairs are merged at the end
+  float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.f, 0.f};
   int qb[2], qe[2];
 #pragma unroll
   for (int r = 0; r < 2; r++) {
@@ -309,15 +300,44 @@ attn_block_kernel(AttnArgs a) {
       qb[r] = __ldg(a.rem_pos + row);
       qe[r] = __ldg(a.rem_pos + row + 1);
     }
-    float mx = -INFINITY;
-    for (int q = qb[r] + t; q < qe[r]; q += 4) mx = fmaxf(mx, rem[q] * scale);
-    mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, 2));
-    const float ms = (mx == -INFINITY) ? 0.f : mx;
-    float s = 0.f;
-    for (int q = qb[r] + t; q < qe[r]; q += 4) s += __expf(rem[q] * scale - ms);
-    M[r] = mx;
-    L[r] = s;
+  }
+  const int rem_len = __reduce_max_sync(FULL, max(qe[0] - qb[0], qe[1] - qb[1]));
+#pragma unroll 1
+  for (int c0 = 0; c0 < rem_len; c0 += 32) {
+    float v[2][8];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int q = qb[r] + c0 + 4 * i + t;
+        v[r][i] = (q < qe[r]) ? rem[q] * scale : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      float cm = v[r][0];
+#pragma unroll
+      for (int i = 1; i < 8; i++) cm = fmaxf(cm, v[r][i]);
+      const float nm = fmaxf(M[r], cm);
+      const float ms = (nm == -INFINITY) ? 0.f : nm;
+      float sum = L[r] * __expf(M[r] - ms);
+#pragma unroll
+      for (int i = 0; i < 8; i++) sum += __expf(v[r][i] - ms);
+      M[r] = nm;
+      L[r] = sum;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+#pragma unroll
+    for (int off = 1; off <= 2; off <<= 1) {
+      const float om = __shfl_xor_sync(FULL, M[r], off), os = __shfl_xor_sync(FULL, L[r], off);
+      const float nm = fmaxf(M[r], om);
+      const float ms = (nm == -INFINITY) ? 0.f : nm;
+      L[r] = L[r] * __expf(M[r] - ms) + os * __expf(om - ms);
+      M[r] = nm;
+    }
+    if (t != 0) L[r] = 0.f;  // from here on L is a per-lane partial sum again
   }
 
   float o[KT][4];
@@ -364,11 +384,12 @@ attn_block_kernel(AttnArgs a) {
       }
       return x;
     };
-    Desc nx = load_desc(kb);
-    load_k(nx.j0);
+    Desc d1 = load_desc(kb);                              // block b at the top of iteration b
+    Desc d2 = (kb + 1 < ke) ? load_desc(kb + 1) : d1;     // block b+1
+    load_k(d1.j0);
 #pragma unroll 1
     for (int b = kb; b < ke; b++) {
-      const Desc cur = nx;
+      const Desc cur = d1;
       const unsigned m0 = cur.m0, m1 = cur.m1;
       // warp-uniform: every entry of the block is stored (the blocks inside a band)
       const bool full = __all_sync(FULL, (m0 & m1) == 0xffffu);
@@ -410,15 +431,15 @@ attn_block_kernel(AttnArgs a) {
           }
         }
       };
-#if ATTN_VEARLY
       load_v();
-#endif
-      // S = Q K^T; main and cross terms accumulate separately: shorter dependent mma chains
-      float c[2][4], x[2][4];
+      // S = Q K^T; the main term and the two cross terms accumulate separately and the two
+      // column tiles alternate: six independent mma chains
+      float c[2][4], x[2][4], y[2][4];
 #pragma unroll
       for (int n = 0; n < 2; n++) {
         c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
         x[n][0] = x[n][1] = x[n][2] = x[n][3] = 0.f;
+        y[n][0] = y[n][1] = y[n][2] = y[n][3] = 0.f;
       }
 #pragma unroll
       for (int q = 0; q < D16 / 2; q++) {
@@ -427,27 +448,25 @@ attn_block_kernel(AttnArgs a) {
           const uint4 qh = sq_hi[warp][4 * q + h][lane], ql = sq_lo[warp][4 * q + h][lane];
           const unsigned ahi[4] = {qh.x, qh.y, qh.z, qh.w};
           const unsigned alo[4] = {ql.x, ql.y, ql.z, ql.w};
+          unsigned bh[2][2], bl[2][2];
 #pragma unroll
           for (int n = 0; n < 2; n++) {
-            const float k0 = kf[n][q].v[2 * h];
-            const float k1 = kf[n][q].v[2 * h + 1];
-            unsigned bh0, bl0, bh1, bl1;
-            attn_split(k0, bh0, bl0);
-            attn_split(k1, bh1, bl1);
-            mma_tf32(x[n], alo, bh0, bh1);
-            mma_tf32(x[n], ahi, bl0, bl1);
-            mma_tf32(c[n], ahi, bh0, bh1);
+            attn_split(kf[n][q].v[2 * h], bh[n][0], bl[n][0]);
+            attn_split(kf[n][q].v[2 * h + 1], bh[n][1], bl[n][1]);
           }
+          mma_tf32(x[0], alo, bh[0][0], bh[0][1]);
+          mma_tf32(x[1], alo, bh[1][0], bh[1][1]);
+          mma_tf32(y[0], ahi, bl[0][0], bl[0][1]);
+          mma_tf32(y[1], ahi, bl[1][0], bl[1][1]);
+          mma_tf32(c[0], ahi, bh[0][0], bh[0][1]);
+          mma_tf32(c[1], ahi, bh[1][0], bh[1][1]);
         }
       }
-      // descriptor and K rows of the next block: in flight during the softmax update and P V
-      if (b + 1 < ke) {
-        nx = load_desc(b + 1);
-        load_k(nx.j0);
-      }
-#if !ATTN_VEARLY
-      load_v();
-#endif
+      // K rows of the next block (its descriptor was read an iteration ago) and the descriptor
+      // of the block after it: in flight during the softmax update and P V
+      d1 = d2;
+      if (b + 1 < ke) load_k(d1.j0);
+      if (b + 2 < ke) d2 = load_desc(b + 2);
       // scaled scores of the stored entries, -inf elsewhere
       float s[2][4];
 #pragma unroll
@@ -455,8 +474,8 @@ attn_block_kernel(AttnArgs a) {
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const int col = 8 * n + 2 * t + e;
-          const float v0 = (c[n][e] + x[n][e]) * scale * w[n][e];
-          const float v1 = (c[n][2 + e] + x[n][2 + e]) * scale * w[n][2 + e];
+          const float v0 = (c[n][e] + (x[n][e] + y[n][e])) * scale * w[n][e];
+          const float v1 = (c[n][2 + e] + (x[n][2 + e] + y[n][2 + e])) * scale * w[n][2 + e];
           s[n][e] = (full || ((m0 >> col) & 1u)) ? v0 : -INFINITY;
           s[n][2 + e] = (full || ((m1 >> col) & 1u)) ? v1 : -INFINITY;
         }
@@ -502,12 +521,21 @@ attn_block_kernel(AttnArgs a) {
         attn_split(s[n][2], ahi[1], alo[1]);  // row g+8, column 8n+2t
         attn_split(s[n][1], ahi[2], alo[2]);  // row g,   column 8n+2t+1 (k-slot t+4)
         attn_split(s[n][3], ahi[3], alo[3]);  // row g+8, column 8n+2t+1
+        // four column tiles at a time, term by term: no mma waits on the one before it
 #pragma unroll
-        for (int u = 0; u < KT; u++) {
-          unsigned bh0, bl0, bh1, bl1;
-          attn_split(vb[n][0][u], bh0, bl0);
-          attn_split(vb[n][1][u], bh1, bl1);
-          mma_3xtf32(o[u], ahi, alo, bh0, bh1, bl0, bl1);
+        for (int u0 = 0; u0 < KT; u0 += 4) {
+          unsigned bh[4][2], bl[4][2];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            attn_split(vb[n][0][u0 + u], bh[u][0], bl[u][0]);
+            attn_split(vb[n][1][u0 + u], bh[u][1], bl[u][1]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) mma_tf32(o[u0 + u], alo, bh[u][0], bh[u][1]);
+#pragma unroll
+          for (int u = 0; u < 4; u++) mma_tf32(o[u0 + u], ahi, bl[u][0], bl[u][1]);
+#pragma unroll
+          for (int u = 0; u < 4; u++) mma_tf32(o[u0 + u], ahi, bh[u][0], bh[u][1]);
         }
       }
     }
@@ -515,6 +543,7 @@ attn_block_kernel(AttnArgs a) {
 
   // O / sum; the remainder scores of the rows become probabilities (their P V terms are added
   // by the gather kernel that follows)
+  float fin_ms[2], fin_inv[2];
 #pragma unroll
   for (int r = 0; r < 2; r++) {
     float sum = L[r];
@@ -535,7 +564,28 @@ attn_block_kernel(AttnArgs a) {
         }
       }
     }
-    for (int q = qb[r] + t; q < qe[r]; q += 4) rem[q] = __expf(rem[q] * scale - ms) * inv;
+    fin_ms[r] = ms;
+    fin_inv[r] = inv;
+  }
+#pragma unroll 1
+  for (int c0 = 0; c0 < rem_len; c0 += 32) {
+    float v[2][8];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int q = qb[r] + c0 + 4 * i + t;
+        v[r][i] = (q < qe[r]) ? rem[q] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int q = qb[r] + c0 + 4 * i + t;
+        if (q < qe[r]) rem[q] = __expf(v[r][i] * scale - fin_ms[r]) * fin_inv[r];
+      }
+    }
   }
 }
 
@@ -660,9 +710,9 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
   a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
   a.stride_rem = rem_nnz;
   a.scale = scale;
-  dim3 grid((unsigned)ceil_div(p.RB, 4), (unsigned)batch);
-  if (d == 32) attn_block_kernel<2><<<grid, 128, 0, st>>>(a);
-  else attn_block_kernel<4><<<grid, 128, 0, st>>>(a);
+  dim3 grid((unsigned)ceil_div(p.RB, kAttnWarps), (unsigned)batch);
+  if (d == 32) attn_block_kernel<2><<<grid, kAttnWarps * 32, 0, st>>>(a);
+  else attn_block_kernel<4><<<grid, kAttnWarps * 32, 0, st>>>(a);
   SB_LAUNCH_CHECK("attn_block_kernel");
   }
   if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_PV))

@@ -74,22 +74,19 @@ __device__ __forceinline__ void transpose_reduce(float (&v)[G], int lane) {
   }
 }
 
-// Partial dot products of one chunk whose entries all share the Q row held in q[]: group entry
-// t of this lane's group goes to part[t].  RAGGED (last chunk of a row or span): entries beyond
-// cnt re-read the chunk's first K row, a valid address, and their result is never stored.
-template <int G, int VEC, int HALF, bool RAGGED>
+// Partial dot products of one full chunk whose 32 entries all share the Q row held in q[]: group
+// entry t of this lane's group goes to part[t].
+template <int G, int VEC, int HALF>
 __device__ __forceinline__ void chunk_dots(float (&part)[G], const float4 (&q)[VEC], int my_j,
                                            const float* __restrict__ K, unsigned ldk, int g0,
-                                           int cnt, const bool (&col_ok)[VEC]) {
-  const int j_first = RAGGED ? __shfl_sync(FULL, my_j, 0) : 0;
+                                           const bool (&col_ok)[VEC]) {
 #pragma unroll
   for (int t0 = 0; t0 < G; t0 += HALF) {
     float4 kv[HALF][VEC];
 #pragma unroll
     for (int u = 0; u < HALF; u++) {
       const int idx = g0 + t0 + u;
-      int j = __shfl_sync(FULL, my_j, idx);
-      if (RAGGED && idx >= cnt) j = j_first;
+      const int j = __shfl_sync(FULL, my_j, idx);
       const float* krow = K + (size_t)((unsigned long long)(unsigned)j * ldk);
 #pragma unroll
       for (int v = 0; v < VEC; v++)
@@ -101,6 +98,44 @@ __device__ __forceinline__ void chunk_dots(float (&part)[G], const float4 (&q)[V
 #pragma unroll
       for (int v = 0; v < VEC; v++) acc = dot4(q[v], kv[u][v], acc);
       part[t0 + u] = acc;
+    }
+  }
+}
+
+// The last, partly filled chunk of a row (ROWWISE): its cnt < 32 entries are dealt round-robin to
+// the 32/G groups (entry e -> group e % (32/G), slot e / (32/G)), so every group has work and the
+// chunk costs ceil(cnt / (32/G)) slots instead of G.  After transpose_reduce lane l of group k
+// owns entry l * (32/G) + k.
+template <int G, int VEC, int HALF>
+__device__ __forceinline__ void chunk_dots_tail(float (&part)[G], const float4 (&q)[VEC], int my_j,
+                                                const float* __restrict__ K, unsigned ldk, int lane,
+                                                int cnt, const bool (&col_ok)[VEC]) {
+  constexpr int NG = 32 / G;
+  const int grp = lane / G;
+  const int nslots = (cnt + NG - 1) / NG;  // warp-uniform
+#pragma unroll
+  for (int t0 = 0; t0 < G; t0 += HALF) {
+    if (t0 < nslots) {
+      float4 kv[HALF][VEC];
+#pragma unroll
+      for (int u = 0; u < HALF; u++) {
+        const int idx = (t0 + u) * NG + grp;  // <= 31
+        const int j = __shfl_sync(FULL, my_j, idx);
+        const float* krow = K + (size_t)((unsigned long long)(unsigned)j * ldk);
+#pragma unroll
+        for (int v = 0; v < VEC; v++)
+          kv[u][v] = (idx < cnt && col_ok[v]) ? ldg4(krow + v * G * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < HALF; u++) {
+        float acc = 0.f;
+#pragma unroll
+        for (int v = 0; v < VEC; v++) acc = dot4(q[v], kv[u][v], acc);
+        part[t0 + u] = acc;
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < HALF; u++) part[t0 + u] = 0.f;
     }
   }
 }
@@ -194,13 +229,17 @@ sddmm_kernel(SddmmArgs a) {
     }
 
     float part[G];
+    bool dealt = false;  // warp-uniform: the chunk's entries were dealt round-robin to the groups
     if (one_row && (ROWWISE || cnt == 32)) {
       // every entry of the chunk shares Q row r0
       if (r0 != q_row) load_q(r0);
       if (!ROWWISE || cnt == 32) {
-        chunk_dots<G, VEC, HALF, false>(part, q, my_j, K, ldk, g0, 32, col_ok);
+        chunk_dots<G, VEC, HALF>(part, q, my_j, K, ldk, g0, col_ok);
       } else {
-        if constexpr (ROWWISE) chunk_dots<G, VEC, HALF, true>(part, q, my_j, K, ldk, g0, cnt, col_ok);
+        if constexpr (ROWWISE) {
+          chunk_dots_tail<G, VEC, HALF>(part, q, my_j, K, ldk, lane, cnt, col_ok);
+          dealt = true;
+        }
       }
     } else {
 #pragma unroll 1
@@ -222,7 +261,14 @@ sddmm_kernel(SddmmArgs a) {
       }
     }
     transpose_reduce<G>(part, lane);
-    if (lane < cnt) out[a.out_compact ? p0 + lane : my_p] = my_s * part[0];
+    if (ROWWISE && dealt) {
+      const int e = l * (32 / G) + lane / G;  // the entry this lane owns
+      const float s_e = __shfl_sync(FULL, my_s, e);
+      const int p_e = __shfl_sync(FULL, (int)my_p, e);
+      if (e < cnt) out[a.out_compact ? p0 + e : (long long)p_e] = s_e * part[0];
+    } else if (lane < cnt) {
+      out[a.out_compact ? p0 + lane : my_p] = my_s * part[0];
+    }
   }
 }
 
