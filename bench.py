@@ -49,9 +49,9 @@ NCU_TRAFFIC_BYTES = {
         "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel
     },
     "one attention call": {
-        "sddmm_kernel": None,
-        "attn_block_kernel": None,
-        "spmm_rows_kernel": None,
+        "sddmm_kernel": 82_586_112,              # scores of the entries outside the blocks
+        "attn_block_kernel": 148_838_144,
+        "spmm_rows_kernel": 99_349_248,          # P V of the entries outside the blocks
     },
 }
 
