@@ -696,12 +696,12 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
     if (rc != SB_OK) return rc;
   }
   if (stages & SB_ATTN_STAGE_BLOCKS) {
-  attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
-  if (mask_val && nnz > 0) {
+  if (mask_val && nnz > 0) {  // (without mask values the kernel never reads the flag)
+    attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
     const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
     attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(mask_val, nnz, flags);
+    SB_LAUNCH_CHECK("attn_mask_ones_kernel");
   }
-  SB_LAUNCH_CHECK("attn_mask_ones_kernel");
   AttnArgs a;
   a.m = (int)m; a.RB = p.RB; a.rb_ptr = p.rb_ptr; a.blk_col = p.blk_col; a.blk_ent = p.blk_ent;
   a.blk_mask = p.blk_mask; a.rem_pos = p.rem_pos; a.mask_val = mask_val; a.mask_is_ones = flags;

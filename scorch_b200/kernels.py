@@ -145,6 +145,18 @@ def attn_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> AttnPlan:
 FUSED_ATTENTION_D = (32, 64)
 
 
+def _mask_is_all_ones(mask_val: torch.Tensor) -> bool:
+    """True when every mask value is exactly 1.0 (a pure pattern mask): multiplying by it is the
+    identity, so the kernels need not read it.  Checked once per tensor (one synchronising
+    reduction) and remembered on the tensor object until it is written in place."""
+    cached = getattr(mask_val, "_sb_all_ones", None)
+    if cached is not None and cached[0] == (mask_val._version, mask_val.data_ptr()):
+        return cached[1]
+    ones = bool((mask_val == 1.0).all().item())
+    mask_val._sb_all_ones = ((mask_val._version, mask_val.data_ptr()), ones)
+    return ones
+
+
 def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
                          attn_plan: Optional[AttnPlan] = None,
                          out: Optional[torch.Tensor] = None, stages: int = 7) -> torch.Tensor:
@@ -169,6 +181,8 @@ def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
         mask_val = _dev(mask_val, torch.float32, "mask_val")
         if mask_val.numel() != nnz:
             raise ValueError("mask_val and crd differ in length")
+        if _mask_is_all_ones(mask_val):
+            mask_val = None
     if attn_plan is None:
         attn_plan = AttnPlan(pos, crd, n=n) if n != m else attn_plan_for(pos, crd)
     if attn_plan.m != m or attn_plan.nnz != nnz or attn_plan.n != n:

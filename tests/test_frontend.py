@@ -102,3 +102,17 @@ def test_sparse_matmul_without_gpu_fails_loudly():
     with pytest.raises(TypeError, match="CUDA tensor"):
         kernels.spmv_csr(torch.zeros(2, dtype=torch.int32), torch.zeros(0, dtype=torch.int32),
                          torch.zeros(0), torch.zeros(1))
+
+
+def test_all_ones_mask_check_is_cached_until_the_tensor_is_written():
+    """The one-call attention path drops mask values that are all exactly 1.0; the check is
+    remembered on the tensor object and redone after an in-place write."""
+    from scorch_b200 import kernels as K
+    v = torch.ones(100)
+    assert K._mask_is_all_ones(v) is True
+    assert v._sb_all_ones[1] is True
+    v[3] = 0.5                      # in-place write bumps the version: the cache entry is stale
+    assert K._mask_is_all_ones(v) is False
+    v[3] = 1.0
+    assert K._mask_is_all_ones(v) is True
+    assert K._mask_is_all_ones(torch.full((4,), 1.0 + 1e-6)) is False
