@@ -36,7 +36,9 @@ constexpr int kDetectSlots = 1024;  // per-warp hash slots for counting entries 
 //   blk_col[capB]     column block of each block
 //   blk_ent[capB*16]  entry index of the first stored entry of (row r of the block)
 //   blk_mask[capB*16] stored columns of (row r of the block), bit c = column 16*blk_col + c
-//   rem_pos[m+1], rem_ent[nnz]   CSR of the entries outside the blocks
+//   rem_pos[m+1], rem_ent[nnz], rem_crd[nnz]   CSR of the entries outside the blocks: entry index
+//                     in the mask and column (a copy, so the gather kernels need not go through
+//                     rem_ent to find it)
 //   cnt[max(RB, m)+1] scratch for the counts, block_sum scan temporaries, total (int64)
 struct AttnPlan {
   int* hdr;
@@ -46,6 +48,7 @@ struct AttnPlan {
   int* blk_mask;
   int* rem_pos;
   int* rem_ent;
+  int* rem_crd;
   int* cnt;
   long long* block_sum;
   long long* total;
@@ -69,6 +72,7 @@ static AttnPlan attn_plan_view(void* base, int64_t m, int64_t nnz) {
   p.blk_mask = reinterpret_cast<int*>(c + off); off += al256((size_t)p.capB * 16 * 4);
   p.rem_pos = reinterpret_cast<int*>(c + off); off += al256((size_t)(m + 1) * 4);
   p.rem_ent = reinterpret_cast<int*>(c + off); off += al256((size_t)(nnz + 1) * 4);
+  p.rem_crd = reinterpret_cast<int*>(c + off); off += al256((size_t)(nnz + 1) * 4);
   const int64_t cn = (m > p.RB ? m : p.RB) + 1;
   p.cnt = reinterpret_cast<int*>(c + off); off += al256((size_t)cn * 4);
   p.block_sum = reinterpret_cast<long long*>(c + off); off += al256((size_t)(ceil_div(cn, 4096) + 1) * 8);
@@ -176,7 +180,7 @@ template <bool FILL>
 __global__ void __launch_bounds__(256)
 attn_rem_kernel(int m, const int* __restrict__ pos, const int* __restrict__ crd,
                 const int* __restrict__ rb_ptr, const int* __restrict__ blk_col, int* __restrict__ cnt,
-                const int* __restrict__ rem_pos, int* __restrict__ rem_ent) {
+                const int* __restrict__ rem_pos, int* __restrict__ rem_ent, int* __restrict__ rem_crd) {
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= m) return;
@@ -186,8 +190,10 @@ attn_rem_kernel(int m, const int* __restrict__ pos, const int* __restrict__ crd,
   for (int p0 = b; p0 < e; p0 += 32) {
     const int p = p0 + lane;
     bool keep = false;
+    int col = 0;
     if (p < e) {
-      const int cb = __ldg(crd + p) >> 4;
+      col = __ldg(crd + p);
+      const int cb = col >> 4;
       int lo = kb, hi = ke;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
@@ -196,7 +202,11 @@ attn_rem_kernel(int m, const int* __restrict__ pos, const int* __restrict__ crd,
       keep = !(lo < ke && __ldg(blk_col + lo) == cb);
     }
     const unsigned mask = __ballot_sync(FULL, keep);
-    if (FILL && keep) rem_ent[outp + __popc(mask & ((1u << lane) - 1))] = p;
+    if (FILL && keep) {
+      const int q = outp + __popc(mask & ((1u << lane) - 1));
+      rem_ent[q] = p;
+      rem_crd[q] = col;
+    }
     outp += __popc(mask);
   }
   if (!FILL && lane == 0) cnt[row] = outp;
@@ -626,13 +636,13 @@ int sb_attn_plan_build(int64_t m, int64_t n, int64_t nnz, const int32_t* pos, co
                                                   p.blk_ent, p.blk_mask);
     SB_LAUNCH_CHECK("attn_detect_kernel<fill>");
     attn_rem_kernel<false><<<(unsigned)ceil_div(m * 32, 256), 256, 0, st>>>((int)m, pos, crd, p.rb_ptr,
-                                                                           p.blk_col, p.cnt, nullptr, nullptr);
+                                                                           p.blk_col, p.cnt, nullptr, nullptr, nullptr);
     SB_LAUNCH_CHECK("attn_rem_kernel<count>");
     rc = exclusive_scan_i32((int)m, p.cnt, p.rem_pos, p.block_sum, p.total, st);
     if (rc != SB_OK) return rc;
     SB_CUDA(cudaMemcpyAsync(&nrem, p.total, 8, cudaMemcpyDeviceToHost, st));
     attn_rem_kernel<true><<<(unsigned)ceil_div(m * 32, 256), 256, 0, st>>>((int)m, pos, crd, p.rb_ptr,
-                                                                          p.blk_col, nullptr, p.rem_pos, p.rem_ent);
+                                                                          p.blk_col, nullptr, p.rem_pos, p.rem_ent, p.rem_crd);
     SB_LAUNCH_CHECK("attn_rem_kernel<fill>");
     SB_CUDA(cudaStreamSynchronize(st));
     int h[2] = {(int)nblk, (int)nrem};
@@ -691,8 +701,9 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
   int* flags = static_cast<int*>(scratch);
   float* rem = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
   if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_SCORES)) {
-    int rc = sddmm_remainder(m, d, rem_nnz, p.rem_pos, p.rem_ent, crd, mask_val, Q, ldq, K, ldk, rem, batch,
-                             stride_q, stride_k, rem_nnz, 1, st);
+    // (columns from the plan's own copy; the entry list is only needed to find the mask values)
+    int rc = sddmm_remainder(m, d, rem_nnz, p.rem_pos, mask_val ? p.rem_ent : nullptr, p.rem_crd, mask_val, Q,
+                             ldq, K, ldk, rem, batch, stride_q, stride_k, rem_nnz, 1, st);
     if (rc != SB_OK) return rc;
   }
   if (stages & SB_ATTN_STAGE_BLOCKS) {
@@ -716,7 +727,7 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
   SB_LAUNCH_CHECK("attn_block_kernel");
   }
   if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_PV))
-    return spmm_remainder(m, d, p.rem_pos, p.rem_ent, crd, rem, V, ldv, nullptr, 0, O, ldo, batch, rem_nnz,
+    return spmm_remainder(m, d, p.rem_pos, nullptr, p.rem_crd, rem, V, ldv, nullptr, 0, O, ldo, batch, rem_nnz,
                           stride_v, stride_o, 1, st);
   return SB_OK;
 }

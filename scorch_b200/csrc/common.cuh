@@ -68,8 +68,9 @@ int exclusive_scan_i32(int n, const int* cnt, int* out, long long* block_sum, lo
 
 // Gather kernels over the entries that a block plan leaves outside its blocks (sddmm.cu /
 // spmm.cu): entries are taken through the list `rem_ent`, rows described by `rem_pos`.
-// out_compact / val_compact: results / values are indexed by position in the list instead of by
-// entry of the original pattern.
+// out_compact: `crd` and the results are indexed by position in the list (the list then only
+// locates the mask values); val_compact: so are the values.  `rem_ent` may be null when the
+// arrays it would index are compact or absent.
 int sddmm_remainder(int64_t m, int64_t d, int64_t rem_nnz, const int* rem_pos, const int* rem_ent,
                     const int* crd, const float* mask_val, const float* Q, int64_t ldq,
                     const float* K, int64_t ldk, float* out, int64_t batch, int64_t stride_q,

@@ -32,7 +32,8 @@ struct SddmmArgs {
   int rowwise;            // one warp per row of pos[] (short rows) instead of one per entry span
   const int* ent;         // optional entry list: entry q of this launch is entry ent[q] of crd /
                           // mask_val / out_val (pos then describes the listed entries per row)
-  int out_compact;        // with ent: result of listed entry q goes to out_val[q], not out_val[ent[q]]
+  int out_compact;        // the launch works on a compact list: crd and out_val are indexed by the
+                          // list position q; ent (if given) only locates mask_val[ent[q]]
   const float* mask_val;  // may be null
   const float* Q;
   long long ldq;
@@ -151,7 +152,8 @@ __device__ __forceinline__ void chunk_dots_tail(float (&part)[G], const float4 (
 template <int G, int VEC, bool EXACT, bool ROWWISE>
 __global__ void __launch_bounds__(kSddmmWarps * 32, (VEC >= 4 || G >= 32) ? 2 : 3)
 sddmm_kernel(SddmmArgs a) {
-  // K rows gathered together
+  // K rows gathered together (8 and 16 loads in flight per lane were measured on the row-wise
+  // launches too and lost to the occupancy they cost)
   constexpr int HALF = (SB_SDDMM_INFLIGHT / VEC < G) ? (SB_SDDMM_INFLIGHT / VEC) : G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long span = (long long)blockIdx.x * kSddmmWarps + warp;
@@ -197,7 +199,7 @@ sddmm_kernel(SddmmArgs a) {
   float next_s = 1.f;
   if (p0 + lane < p_end) {
     next_p = a.ent ? (long long)ld_stream(a.ent + p0 + lane) : p0 + lane;
-    next_j = ld_stream(a.crd + next_p);
+    next_j = ld_stream(a.crd + (a.out_compact ? p0 + lane : next_p));
     if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
     if (a.row) next_i = ld_stream(a.row + next_p);
   }
@@ -210,7 +212,7 @@ sddmm_kernel(SddmmArgs a) {
     const long long my_p = next_p;
     if (p0 + 32 + lane < p_end) {
       next_p = a.ent ? (long long)ld_stream(a.ent + p0 + 32 + lane) : p0 + 32 + lane;
-      next_j = ld_stream(a.crd + next_p);
+      next_j = ld_stream(a.crd + (a.out_compact ? p0 + 32 + lane : next_p));
       if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
       if (a.row) next_i = ld_stream(a.row + next_p);
     }

@@ -144,6 +144,7 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
         }
       }
     } else {
+      // (batching these loads like the full chunk's, predicated on the count, measured slower)
       for (int t0 = 0; t0 < cnt; t0 += G) {
         const int t = t0 + g;
         const unsigned j = (unsigned)__shfl_sync(FULL, my_j, t & 31);

@@ -72,42 +72,54 @@ def gcn_forward(pos, crd, val, X, W1, W2, plan: Optional[K.CsrPlan] = None) -> t
 
 class HostSparseAttention:
     """``sparse_attention`` for operands that live in (pinned) host memory, as the reference's
-    callers hold them: the (batch*heads) units are cut into chunks and pipelined over three
-    streams — host->device copy of chunk c+1, kernels of chunk c and device->host copy of chunk
-    c-1 overlap, so a step costs about the PCIe time of its inputs instead of copy + compute."""
+    callers hold them: the (batch*heads) units are cut into chunks and pipelined over copy and
+    compute streams — host->device copies of chunk c+1, kernels of chunk c and device->host copy
+    of chunk c-1 overlap, so a step costs about the PCIe time of its inputs instead of copy +
+    compute.  The chunks shrink towards the end (weights 7:5:3:1 for four chunks): what cannot
+    overlap is the last chunk's kernels and its copy back, so that chunk is the smallest.
+    Measured on B200 (32 heads, 100 MB in, 34 MB out): 2.22 ms with shrinking chunks against 2.29
+    with equal ones; Q, K and V on a copy stream each (``copy_streams=3``) was slower, 2.43 ms."""
 
     def __init__(self, pos, crd, mask_val, units: int, seq: int, d: int, chunks: int = 4,
-                 scale: float = 1.0):
+                 scale: float = 1.0, shrink: bool = True, copy_streams: int = 1):
         dev = pos.device
         self.pos, self.crd, self.mask_val, self.scale = pos, crd, mask_val, scale
         self.units, self.seq, self.d = units, seq, d
         self.plan = K.plan_for(pos, crd.numel())
         self.attn_plan = attention_plan(pos, crd, d, d)
         self.block_plan = None if self.attn_plan else attention_block_plan(pos, crd)
-        self.bounds = [units * c // chunks for c in range(chunks + 1)]
+        weights = [2 * (chunks - c) - 1 if shrink else 1 for c in range(chunks)]   # 7, 5, 3, 1
+        acc, self.bounds = 0, [0]
+        for w in weights:
+            acc += w
+            self.bounds.append(max(self.bounds[-1], min(units, round(units * acc / sum(weights)))))
+        self.bounds[-1] = units
         self.dev = [torch.empty((units, seq, d), dtype=torch.float32, device=dev) for _ in range(3)]
         self.scores = (None if self.attn_plan else
                        torch.empty((units, crd.numel()), dtype=torch.float32, device=dev))
         self.out = torch.empty((units, seq, d), dtype=torch.float32, device=dev)
-        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        ins = [torch.cuda.Stream(device=dev) for _ in range(copy_streams)]
+        self.s_in = [ins[i % copy_streams] for i in range(3)]
+        self.s_out = torch.cuda.Stream(device=dev)
 
     def __call__(self, Qh: torch.Tensor, Kh: torch.Tensor, Vh: torch.Tensor,
                  out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
         if out_host is None:
             out_host = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, pin_memory=True)
         main = torch.cuda.current_stream()
-        self.s_in.wait_stream(main)      # earlier work on these buffers is done
+        for st in self.s_in:             # earlier work on these buffers is done
+            st.wait_stream(main)
         self.s_out.wait_stream(main)
         for c in range(len(self.bounds) - 1):
             u0, u1 = self.bounds[c], self.bounds[c + 1]
             if u0 == u1:
                 continue
-            with torch.cuda.stream(self.s_in):
-                for dst, src in zip(self.dev, (Qh, Kh, Vh)):
+            for st, dst, src in zip(self.s_in, self.dev, (Qh, Kh, Vh)):
+                with torch.cuda.stream(st):
                     dst[u0:u1].copy_(src[u0:u1], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record(self.s_in)
-            main.wait_event(arrived)
+                    arrived = torch.cuda.Event()
+                    arrived.record(st)
+                main.wait_event(arrived)
             if self.attn_plan:
                 K.sparse_attention_csr(self.pos, self.crd, self.mask_val, self.dev[0][u0:u1],
                                        self.dev[1][u0:u1], self.dev[2][u0:u1], scale=self.scale,
