@@ -57,6 +57,7 @@ __device__ __forceinline__ int advance_row(const int* __restrict__ pos, int m, i
 }
 
 constexpr int kChunksPerWarp = 8;  // a warp owns 8 consecutive 32-entry chunks: one row search
+constexpr int kRowsPerWarp = 4;    // row-wise launches: consecutive rows per warp
 
 // Sums G per-lane partial values for G entries across the G lanes of a group with G-1 shuffles
 // (a butterfly that halves the number of live values per lane at every step).  On return lane l
@@ -147,8 +148,9 @@ __device__ __forceinline__ void chunk_dots_tail(float (&part)[G], const float4 (
 // partial dots per lane and transpose-reduces them, after which lane t of the warp owns entry t
 // of the chunk.  Full chunks that lie inside one mask row take a path without per-entry row
 // bookkeeping or predicates.
-// ROWWISE: one warp per mask row instead of one per entry span (used for the short rows of a
-// block plan's remainder list, where spans would cross a row boundary in almost every chunk).
+// ROWWISE: one warp per kRowsPerWarp mask rows, row by row, instead of one per entry span (used
+// for the short rows of a block plan's remainder list, where spans would cross a row boundary in
+// almost every chunk).
 template <int G, int VEC, bool EXACT, bool ROWWISE>
 __global__ void __launch_bounds__(kSddmmWarps * 32, (VEC >= 4 || G >= 32) ? 2 : 3)
 sddmm_kernel(SddmmArgs a) {
@@ -157,12 +159,28 @@ sddmm_kernel(SddmmArgs a) {
   constexpr int HALF = (SB_SDDMM_INFLIGHT / VEC < G) ? (SB_SDDMM_INFLIGHT / VEC) : G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long span = (long long)blockIdx.x * kSddmmWarps + warp;
-  long long p0, p_end;
+  long long p0 = 0, p_end = 0;
+  // row-wise: the warp takes kRowsPerWarp consecutive rows; their bounds and first index chunks
+  // are fetched together, so the rows share one start-up latency instead of paying it each
+  constexpr int R = ROWWISE ? kRowsPerWarp : 1;
+  int pb = 0;                 // lane r <= R: pos[first row + r]
+  int first_j[R];
+  long long first_p[R];
+  float first_s[R];
   if (ROWWISE) {
-    if (span >= a.m) return;
-    p0 = __ldg(a.pos + span);
-    p_end = __ldg(a.pos + span + 1);
-    if (p0 == p_end) return;
+    const long long row_base = span * R;
+    if (row_base >= a.m) return;
+    if (lane <= R) pb = __ldg(a.pos + min(row_base + lane, (long long)a.m));
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int b = __shfl_sync(FULL, pb, r), e = __shfl_sync(FULL, pb, r + 1);
+      first_j[r] = 0; first_p[r] = 0; first_s[r] = 1.f;
+      if (b + lane < e) {
+        first_p[r] = a.ent ? (long long)ld_stream(a.ent + b + lane) : b + lane;
+        first_j[r] = ld_stream(a.crd + (a.out_compact ? b + lane : first_p[r]));
+        if (a.mask_val) first_s[r] = ld_stream(a.mask_val + first_p[r]);
+      }
+    }
   } else {
     p0 = span * (32 * kChunksPerWarp);
     if (p0 >= a.nnz) return;
@@ -182,7 +200,7 @@ sddmm_kernel(SddmmArgs a) {
 #pragma unroll
   for (int v = 0; v < VEC; v++) q[v] = make_float4(0.f, 0.f, 0.f, 0.f);
   int q_row = -1;
-  int r0 = ROWWISE ? (int)span : (a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0);
+  int r0 = ROWWISE ? 0 : (a.pos ? row_of_entry(a.pos, 0, a.m, (int)p0) : 0);
 
   auto load_q = [&](int row) {
     q_row = row;
@@ -197,11 +215,23 @@ sddmm_kernel(SddmmArgs a) {
   int next_j = 0, next_i = 0;
   long long next_p = 0;
   float next_s = 1.f;
-  if (p0 + lane < p_end) {
+  if (!ROWWISE && p0 + lane < p_end) {
     next_p = a.ent ? (long long)ld_stream(a.ent + p0 + lane) : p0 + lane;
     next_j = ld_stream(a.crd + (a.out_compact ? p0 + lane : next_p));
     if (a.mask_val) next_s = ld_stream(a.mask_val + next_p);
     if (a.row) next_i = ld_stream(a.row + next_p);
+  }
+#pragma unroll 1
+  for (int rr = 0; rr < R; rr++) {
+  if (ROWWISE) {
+    // this row's bounds and first chunk (select chains: the arrays stay in registers)
+    p0 = __shfl_sync(FULL, pb, rr);
+    p_end = __shfl_sync(FULL, pb, rr + 1);
+    r0 = (int)(span * R) + rr;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      if (r == rr) { next_j = first_j[r]; next_p = first_p[r]; next_s = first_s[r]; }
+    }
   }
 #pragma unroll 1
   for (; p0 < p_end; p0 += 32) {
@@ -272,6 +302,7 @@ sddmm_kernel(SddmmArgs a) {
       out[a.out_compact ? p0 + lane : my_p] = my_s * part[0];
     }
   }
+  }
 }
 
 // Any d / any alignment: one lane per entry, scalar loop over d.
@@ -296,7 +327,7 @@ template <int G, int VEC>
 static int launch_sddmm(const SddmmArgs& a, int64_t batch, cudaStream_t st) {
   const bool exact = a.d == G * VEC * 4;
   if (a.rowwise && a.pos) {
-    dim3 grid((unsigned)ceil_div(a.m, kSddmmWarps), (unsigned)batch);
+    dim3 grid((unsigned)ceil_div(ceil_div(a.m, kRowsPerWarp), kSddmmWarps), (unsigned)batch);
     if (exact) sddmm_kernel<G, VEC, true, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
     else sddmm_kernel<G, VEC, false, true><<<grid, kSddmmWarps * 32, 0, st>>>(a);
   } else {

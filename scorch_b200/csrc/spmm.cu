@@ -40,6 +40,7 @@ struct SpmmArgs {
   const int* ent;  // optional entry list: entry p of pos[] is entry ent[p] of crd / val
   int val_compact; // with ent: the value of listed entry p is val[p], not val[ent[p]]
   int accumulate;  // add to the existing contents of C (before bias / ReLU)
+  int short_rows;  // many rows of a few dozen entries: several rows per warp
 };
 
 // W floats (4 = 128-bit, 8 = 256-bit) moved by one load/store instruction.
@@ -89,14 +90,15 @@ __device__ __forceinline__ void accumulate_range(Pack<W> (&acc)[VEC], const int*
                                                  const float* __restrict__ Bcol, unsigned ldb,
                                                  int b, int e, int lane, const bool (&col_ok)[VEC],
                                                  const int* __restrict__ ent = nullptr,
-                                                 bool val_compact = false) {
+                                                 bool val_compact = false, bool have_first = false,
+                                                 int first_j = 0, float first_a = 0.f) {
   constexpr int G = 32 / L;
   const int g = lane / L;
   // software pipeline: the next chunk's indices/values are in flight while this chunk's rows of
-  // the dense operand are gathered
-  int next_j = 0;
-  float next_a = 0.f;
-  if (b + lane < e) {
+  // the dense operand are gathered (the caller may have fetched the first chunk already)
+  int next_j = first_j;
+  float next_a = first_a;
+  if (!have_first && b + lane < e) {
     const int x = ent ? ld_stream(ent + b + lane) : b + lane;
     next_j = ld_stream(crd + x);
     next_a = ld_stream(val + (val_compact ? b + lane : x));
@@ -193,45 +195,80 @@ __device__ __forceinline__ Pack<W> epilogue(Pack<W> s, const float* bias, int co
   return s;
 }
 
-// One warp per row; grid = (row blocks, column tiles, batch).
-template <int L, int VEC, int W, bool EXACT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+// One warp per R consecutive rows; grid = (row blocks, column tiles, batch).  R = 1 in general;
+// launches over many short rows (the entries a block plan leaves outside its blocks) use R = 4:
+// the rows' bounds and first index chunks are fetched together, so the rows share one start-up
+// latency instead of paying it each.
+constexpr int kShortRowsPerWarp = 4;
+template <int L, int VEC, int W, bool EXACT, int R>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, R > 1 ? 4 : 1)
 spmm_rows_kernel(SpmmArgs a) {
   constexpr int TILE = L * W * VEC;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * kWarpsPerCta + warp;
-  if (row >= a.m) return;
-  const int b = __ldg(a.pos + row), e = __ldg(a.pos + row + 1);
-  if (a.skip_heavy && e - b > SB_HEAVY_ROW_NNZ) return;
+  const int row_base = (blockIdx.x * kWarpsPerCta + warp) * R;
+  if (row_base >= a.m) return;
   const long long bz = blockIdx.z;
   const int l = lane % L;
   const int col0 = blockIdx.y * TILE + l * W;
+  const float* val = a.val + bz * a.stride_val;
   bool col_ok[VEC];
-  Pack<W> acc[VEC];
 #pragma unroll
-  for (int v = 0; v < VEC; v++) {
-    col_ok[v] = EXACT || (col0 + v * L * W) < a.k;
+  for (int v = 0; v < VEC; v++) col_ok[v] = EXACT || (col0 + v * L * W) < a.k;
+  int pb = 0;  // lane r <= R: pos[row_base + r] (rows past the end read pos[m]: empty)
+  if (lane <= R) pb = __ldg(a.pos + min(row_base + lane, a.m));
+  int first_j[R];
+  float first_a[R];
+  if (R > 1) {
 #pragma unroll
-    for (int w = 0; w < W; w++) acc[v].v[w] = 0.f;
+    for (int r = 0; r < R; r++) {
+      const int b = __shfl_sync(FULL, pb, r), e = __shfl_sync(FULL, pb, r + 1);
+      first_j[r] = 0;
+      first_a[r] = 0.f;
+      if (b + lane < e) {
+        const int x = a.ent ? ld_stream(a.ent + b + lane) : b + lane;
+        first_j[r] = ld_stream(a.crd + x);
+        first_a[r] = ld_stream(val + (a.val_compact ? b + lane : x));
+      }
+    }
   }
-  accumulate_range<L, VEC, W, EXACT>(acc, a.crd, a.val + bz * a.stride_val,
-                                           a.B + bz * a.stride_b + col0, (unsigned)a.ldb, b, e,
-                                           lane, col_ok, a.ent, a.val_compact != 0);
-  reduce_groups<L, VEC, W>(acc);
-  if (lane < L) {
-    float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
+#pragma unroll 1
+  for (int rr = 0; rr < R; rr++) {
+    const int row = row_base + rr;
+    if (row >= a.m) break;
+    const int b = __shfl_sync(FULL, pb, rr), e = __shfl_sync(FULL, pb, rr + 1);
+    if (a.skip_heavy && e - b > SB_HEAVY_ROW_NNZ) continue;
+    Pack<W> acc[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
-      const int col = col0 + v * L * W;
-      if (!col_ok[v]) continue;
-      if (a.accumulate) {
 #pragma unroll
-        for (int w = 0; w < W; w += 4) {
-          const float4 old = *reinterpret_cast<const float4*>(crow + col + w);
-          acc[v].v[w] += old.x; acc[v].v[w + 1] += old.y; acc[v].v[w + 2] += old.z; acc[v].v[w + 3] += old.w;
-        }
+      for (int w = 0; w < W; w++) acc[v].v[w] = 0.f;
+    }
+    int fj = 0;
+    float fa = 0.f;
+    if (R > 1) {
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        if (r == rr) { fj = first_j[r]; fa = first_a[r]; }
       }
-      st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
+    }
+    accumulate_range<L, VEC, W, EXACT>(acc, a.crd, val, a.B + bz * a.stride_b + col0, (unsigned)a.ldb,
+                                             b, e, lane, col_ok, a.ent, a.val_compact != 0, R > 1, fj, fa);
+    reduce_groups<L, VEC, W>(acc);
+    if (lane < L) {
+      float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
+#pragma unroll
+      for (int v = 0; v < VEC; v++) {
+        const int col = col0 + v * L * W;
+        if (!col_ok[v]) continue;
+        if (a.accumulate) {
+#pragma unroll
+          for (int w = 0; w < W; w += 4) {
+            const float4 old = *reinterpret_cast<const float4*>(crow + col + w);
+            acc[v].v[w] += old.x; acc[v].v[w + 1] += old.y; acc[v].v[w + 2] += old.z; acc[v].v[w + 3] += old.w;
+          }
+        }
+        st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
+      }
     }
   }
 }
@@ -363,8 +400,13 @@ static int launch_vec2(const SpmmArgs& a, int64_t batch, const void* plan, int64
                        int64_t plan_segments, void* scratch, cudaStream_t st) {
   constexpr int TILE = L * W * VEC;
   const unsigned tiles = (unsigned)ceil_div(a.k, TILE);
-  dim3 grid((unsigned)ceil_div(a.m, kWarpsPerCta), tiles, (unsigned)batch);
-  spmm_rows_kernel<L, VEC, W, EXACT><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  if (a.short_rows) {
+    dim3 grid((unsigned)ceil_div(ceil_div(a.m, kShortRowsPerWarp), kWarpsPerCta), tiles, (unsigned)batch);
+    spmm_rows_kernel<L, VEC, W, EXACT, kShortRowsPerWarp><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  } else {
+    dim3 grid((unsigned)ceil_div(a.m, kWarpsPerCta), tiles, (unsigned)batch);
+    spmm_rows_kernel<L, VEC, W, EXACT, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  }
   SB_LAUNCH_CHECK("spmm_rows_kernel");
   if (plan && plan_segments != 0) {
     PlanView pv = plan_view(plan, nnz);
@@ -442,7 +484,7 @@ int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent,
   a.m = (int)m; a.k = (int)k; a.pos = rem_pos; a.crd = crd; a.val = val; a.B = B; a.ldb = ldb;
   a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
   a.stride_val = stride_val; a.stride_b = stride_b; a.stride_c = stride_c;
-  a.skip_heavy = 0; a.ent = rem_ent; a.val_compact = val_compact; a.accumulate = 1;
+  a.skip_heavy = 0; a.ent = rem_ent; a.val_compact = val_compact; a.accumulate = 1; a.short_rows = 1;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, nullptr, 0, 0, nullptr, st);
 }
 
@@ -510,6 +552,7 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
   a.ent = nullptr;
   a.val_compact = 0;
   a.accumulate = 0;
+  a.short_rows = 0;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, plan, nnz, plan_segments, scratch, st);
 }
 
