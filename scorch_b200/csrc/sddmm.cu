@@ -57,7 +57,7 @@ __device__ __forceinline__ int advance_row(const int* __restrict__ pos, int m, i
 }
 
 constexpr int kChunksPerWarp = 8;  // a warp owns 8 consecutive 32-entry chunks: one row search
-constexpr int kRowsPerWarp = 4;    // row-wise launches: consecutive rows per warp
+constexpr int kRowsPerWarp = 4;   // row-wise launches: consecutive rows per warp (2, 8 measured slower)
 
 // Sums G per-lane partial values for G entries across the G lanes of a group with G-1 shuffles
 // (a butterfly that halves the number of live values per lane at every step).  On return lane l
