@@ -59,7 +59,7 @@ def test_attn_plan_matches_dense_scan(rows, cols, window, density):
 @pytest.mark.parametrize("d", [32, 64])
 @pytest.mark.parametrize("rows,cols,window,density,empty", [
     (500, 500, 30, 0.02, (3, 17, 250)),     # band + scattered entries, a ragged last row block
-    (256, 256, 40, 0.0, ()),                 # blocks only: every entry of the band edges is masked in
+    (256, 256, 40, 0.0, ()),                 # band only: full blocks, masked edge blocks, a few edge entries gathered
     (300, 300, 0, 0.05, (0,)),               # no blocks at all: everything goes through the gather kernels
     (128, 640, 24, 0.01, ()),                # K / V longer than Q
 ])
@@ -167,3 +167,46 @@ def test_sparse_attention_rejects_bad_arguments():
     with pytest.raises(Exception) as e:
         K.sparse_attention_csr(dev(pos), dev(crd), None, x, x, x, attn_plan=ap, stages=0)
     assert "stage" in str(e.value)
+
+
+def test_sparse_attention_without_scattered_entries(oracle):
+    """A block-diagonal mask: every entry lies in a fully stored block, nothing is left for the
+    gather kernels (rem_nnz == 0, the scratch holds the flags only)."""
+    from scorch_b200 import kernels as K
+    rows = 192
+    dense = np.zeros((rows, rows), dtype=bool)
+    for b in range(0, rows, 32):
+        dense[b:b + 32, b:b + 32] = True
+    pos = np.concatenate([[0], np.cumsum(dense.sum(1))]).astype(np.int32)
+    crd = np.nonzero(dense)[1].astype(np.int32)
+    rng = np.random.default_rng(0)
+    mval = rng.uniform(0.5, 1.5, len(crd)).astype(np.float32)
+    Q, Km, V = (rng.standard_normal((2, rows, 32)).astype(np.float32) for _ in range(3))
+    ap = K.AttnPlan(dev(pos), dev(crd))
+    assert ap.rem_nnz == 0 and ap.blocks == 6 * 4
+    got = K.sparse_attention_csr(dev(pos), dev(crd), dev(mval), dev(Q), dev(Km), dev(V), scale=0.2, attn_plan=ap)
+    for u in range(2):
+        want = oracle_attention(oracle, pos, crd, mval, Q[u], Km[u], V[u], 0.2)
+        ok, err, bad = oracle.allclose_report(got[u].cpu().numpy(), want, RTOL, ATOL)
+        assert ok, (u, err, bad)
+
+
+def test_sparse_attention_wide_rows_fall_back_to_the_gather_kernels(oracle):
+    """Row blocks that touch more column blocks than the plan's counting table holds keep no
+    blocks: their (long) rows go through the gather kernels, chunk after chunk."""
+    from scorch_b200 import kernels as K
+    rows, cols, d = 48, 20000, 64
+    rng = np.random.default_rng(3)
+    dense = rng.random((rows, cols)) < 0.06          # ~1200 entries per row, all 1250 column blocks touched
+    dense[:, :64] = True                             # plus a dense stripe that would qualify as blocks
+    pos = np.concatenate([[0], np.cumsum(dense.sum(1))]).astype(np.int32)
+    crd = np.nonzero(dense)[1].astype(np.int32)
+    Q = (rng.standard_normal((rows, d)) * 0.5).astype(np.float32)
+    Km = (rng.standard_normal((cols, d)) * 0.5).astype(np.float32)
+    V = rng.standard_normal((cols, d)).astype(np.float32)
+    ap = K.AttnPlan(dev(pos), dev(crd), n=cols)
+    assert ap.blocks == 0 and ap.rem_nnz == len(crd)
+    got = K.sparse_attention_csr(dev(pos), dev(crd), None, dev(Q), dev(Km), dev(V), scale=0.125, attn_plan=ap)
+    want = oracle_attention(oracle, pos, crd, None, Q, Km, V, 0.125)
+    ok, err, bad = oracle.allclose_report(got.cpu().numpy(), want, RTOL, ATOL)
+    assert ok, (err, bad)
