@@ -263,6 +263,12 @@ __device__ __forceinline__ void attn_split(float x, unsigned& hi, unsigned& lo) 
   hi = __float_as_uint(x) & 0xffffe000u;
   lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
 }
+// 2^x on the special-function unit (ex2.approx: 2 ulp; 2^-inf = 0)
+__device__ __forceinline__ float attn_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // 256-bit read-only load (32-byte aligned): one instruction covers whole 128-byte lines of the
 // K / V rows, half the L1 wavefronts of 128-bit loads
 struct Float8 { float v[8]; };
@@ -294,7 +300,7 @@ attn_block_kernel(AttnArgs a) {
   float* rem = a.rem + bz * a.stride_rem;
   const int i0 = rb * 16;
   const int kb = __ldg(a.rb_ptr + rb), ke = __ldg(a.rb_ptr + rb + 1);
-  const float scale = a.scale;
+  const float scale = a.scale * 1.4426950408889634f;  // scores are kept in log2 units: exp2 below
   const float* mask_val = (a.mask_val && !__ldg(a.mask_is_ones)) ? a.mask_val : nullptr;
 
   // running maximum M and (per-thread partial) sum L of both rows, started from the rows'
@@ -330,9 +336,9 @@ attn_block_kernel(AttnArgs a) {
       for (int i = 1; i < 8; i++) cm = fmaxf(cm, v[r][i]);
       const float nm = fmaxf(M[r], cm);
       const float ms = (nm == -INFINITY) ? 0.f : nm;
-      float sum = L[r] * __expf(M[r] - ms);
+      float sum = L[r] * attn_exp2(M[r] - ms);
 #pragma unroll
-      for (int i = 0; i < 8; i++) sum += __expf(v[r][i] - ms);
+      for (int i = 0; i < 8; i++) sum += attn_exp2(v[r][i] - ms);
       M[r] = nm;
       L[r] = sum;
     }
@@ -344,7 +350,7 @@ attn_block_kernel(AttnArgs a) {
       const float om = __shfl_xor_sync(FULL, M[r], off), os = __shfl_xor_sync(FULL, L[r], off);
       const float nm = fmaxf(M[r], om);
       const float ms = (nm == -INFINITY) ? 0.f : nm;
-      L[r] = L[r] * __expf(M[r] - ms) + os * __expf(om - ms);
+      L[r] = L[r] * attn_exp2(M[r] - ms) + os * attn_exp2(om - ms);
       M[r] = nm;
     }
     if (t != 0) L[r] = 0.f;  // from here on L is a per-lane partial sum again
@@ -442,14 +448,12 @@ attn_block_kernel(AttnArgs a) {
         }
       };
       load_v();
-      // S = Q K^T; the main term and the two cross terms accumulate separately and the two
-      // column tiles alternate: six independent mma chains
-      float c[2][4], x[2][4], y[2][4];
+      // S = Q K^T; main and cross terms accumulate separately, the two column tiles alternate
+      float c[2][4], x[2][4];
 #pragma unroll
       for (int n = 0; n < 2; n++) {
         c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
         x[n][0] = x[n][1] = x[n][2] = x[n][3] = 0.f;
-        y[n][0] = y[n][1] = y[n][2] = y[n][3] = 0.f;
       }
 #pragma unroll
       for (int q = 0; q < D16 / 2; q++) {
@@ -466,8 +470,8 @@ attn_block_kernel(AttnArgs a) {
           }
           mma_tf32(x[0], alo, bh[0][0], bh[0][1]);
           mma_tf32(x[1], alo, bh[1][0], bh[1][1]);
-          mma_tf32(y[0], ahi, bl[0][0], bl[0][1]);
-          mma_tf32(y[1], ahi, bl[1][0], bl[1][1]);
+          mma_tf32(x[0], ahi, bl[0][0], bl[0][1]);
+          mma_tf32(x[1], ahi, bl[1][0], bl[1][1]);
           mma_tf32(c[0], ahi, bh[0][0], bh[0][1]);
           mma_tf32(c[1], ahi, bh[1][0], bh[1][1]);
         }
@@ -482,12 +486,24 @@ attn_block_kernel(AttnArgs a) {
 #pragma unroll
       for (int n = 0; n < 2; n++) {
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int col = 8 * n + 2 * t + e;
-          const float v0 = (c[n][e] + (x[n][e] + y[n][e])) * scale * w[n][e];
-          const float v1 = (c[n][2 + e] + (x[n][2 + e] + y[n][2 + e])) * scale * w[n][2 + e];
-          s[n][e] = (full || ((m0 >> col) & 1u)) ? v0 : -INFINITY;
-          s[n][2 + e] = (full || ((m1 >> col) & 1u)) ? v1 : -INFINITY;
+        for (int e = 0; e < 4; e++) s[n][e] = (c[n][e] + x[n][e]) * scale;
+      }
+      if (mask_val) {
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) s[n][e] *= w[n][e];
+        }
+      }
+      if (!full) {
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int col = 8 * n + 2 * t + e;
+            if (!((m0 >> col) & 1u)) s[n][e] = -INFINITY;
+            if (!((m1 >> col) & 1u)) s[n][2 + e] = -INFINITY;
+          }
         }
       }
       // running softmax of rows g (r = 0) and g+8 (r = 1)
@@ -499,14 +515,14 @@ attn_block_kernel(AttnArgs a) {
         bm = fmaxf(bm, __shfl_xor_sync(FULL, bm, 2));
         const float nm = fmaxf(M[r], bm);
         const float ms = (nm == -INFINITY) ? 0.f : nm;
-        alpha[r] = __expf(M[r] - ms);  // 0 while the row has seen no entry
+        alpha[r] = attn_exp2(M[r] - ms);  // 0 while the row has seen no entry
         M[r] = nm;
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; n++) {
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const float p = __expf(s[n][2 * r + e] - ms);
+            const float p = attn_exp2(s[n][2 * r + e] - ms);
             s[n][2 * r + e] = p;
             sum += p;
           }
@@ -593,7 +609,7 @@ attn_block_kernel(AttnArgs a) {
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const int q = qb[r] + c0 + 4 * i + t;
-        if (q < qe[r]) rem[q] = __expf(v[r][i] * scale - fin_ms[r]) * fin_inv[r];
+        if (q < qe[r]) rem[q] = attn_exp2(v[r][i] * scale - fin_ms[r]) * fin_inv[r];
       }
     }
   }
