@@ -200,6 +200,7 @@ __device__ __forceinline__ Pack<W> epilogue(Pack<W> s, const float* bias, int co
 // the rows' bounds and first index chunks are fetched together, so the rows share one start-up
 // latency instead of paying it each.
 constexpr int kShortRowsPerWarp = 4;  // (2 and 8 measured slower)
+// (four CTAs per SM for the short-row form: 64 registers; five and three measured slower)
 template <int L, int VEC, int W, bool EXACT, int R>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, R > 1 ? 4 : 1)
 spmm_rows_kernel(SpmmArgs a) {
