@@ -723,24 +723,24 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
     if (rc != SB_OK) return rc;
   }
   if (stages & SB_ATTN_STAGE_BLOCKS) {
-  if (mask_val && nnz > 0) {  // (without mask values the kernel never reads the flag)
-    attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
-    const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
-    attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(mask_val, nnz, flags);
-    SB_LAUNCH_CHECK("attn_mask_ones_kernel");
-  }
-  AttnArgs a;
-  a.m = (int)m; a.RB = p.RB; a.rb_ptr = p.rb_ptr; a.blk_col = p.blk_col; a.blk_ent = p.blk_ent;
-  a.blk_mask = p.blk_mask; a.rem_pos = p.rem_pos; a.mask_val = mask_val; a.mask_is_ones = flags;
-  a.Q = Q; a.K = K; a.V = V; a.O = O; a.rem = rem;
-  a.ldq = (unsigned)ldq; a.ldk = (unsigned)ldk; a.ldv = (unsigned)ldv; a.ldo = ldo;
-  a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
-  a.stride_rem = rem_nnz;
-  a.scale = scale;
-  dim3 grid((unsigned)ceil_div(p.RB, kAttnWarps), (unsigned)batch);
-  if (d == 32) attn_block_kernel<2><<<grid, kAttnWarps * 32, 0, st>>>(a);
-  else attn_block_kernel<4><<<grid, kAttnWarps * 32, 0, st>>>(a);
-  SB_LAUNCH_CHECK("attn_block_kernel");
+    if (mask_val && nnz > 0) {  // (without mask values the kernel never reads the flag)
+      attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
+      const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
+      attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(mask_val, nnz, flags);
+      SB_LAUNCH_CHECK("attn_mask_ones_kernel");
+    }
+    AttnArgs a;
+    a.m = (int)m; a.RB = p.RB; a.rb_ptr = p.rb_ptr; a.blk_col = p.blk_col; a.blk_ent = p.blk_ent;
+    a.blk_mask = p.blk_mask; a.rem_pos = p.rem_pos; a.mask_val = mask_val; a.mask_is_ones = flags;
+    a.Q = Q; a.K = K; a.V = V; a.O = O; a.rem = rem;
+    a.ldq = (unsigned)ldq; a.ldk = (unsigned)ldk; a.ldv = (unsigned)ldv; a.ldo = ldo;
+    a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
+    a.stride_rem = rem_nnz;
+    a.scale = scale;
+    dim3 grid((unsigned)ceil_div(p.RB, kAttnWarps), (unsigned)batch);
+    if (d == 32) attn_block_kernel<2><<<grid, kAttnWarps * 32, 0, st>>>(a);
+    else attn_block_kernel<4><<<grid, kAttnWarps * 32, 0, st>>>(a);
+    SB_LAUNCH_CHECK("attn_block_kernel");
   }
   if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_PV))
     return spmm_remainder(m, d, p.rem_pos, nullptr, p.rem_crd, rem, V, ldv, nullptr, 0, O, ldo, batch, rem_nnz,
