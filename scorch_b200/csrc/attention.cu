@@ -447,7 +447,6 @@ attn_block_kernel(AttnArgs a) {
           }
         }
       };
-      load_v();
       // S = Q K^T; main and cross terms accumulate separately, the two column tiles alternate
       float c[2][4], x[2][4];
 #pragma unroll
@@ -481,6 +480,9 @@ attn_block_kernel(AttnArgs a) {
       d1 = d2;
       if (b + 1 < ke) load_k(d1.j0);
       if (b + 2 < ke) d2 = load_desc(b + 2);
+      // the V rows of this block: in flight during the softmax update (issuing them before S
+      // keeps 32 more registers live through it and measured 3 % slower)
+      load_v();
       // scaled scores of the stored entries, -inf elsewhere
       float s[2][4];
 #pragma unroll
