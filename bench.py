@@ -504,7 +504,14 @@ class GcnSharded:
         return {"spmm_layer1_k256": per(256), "spmm_layer2_k64": per(64)}
 
     kernels = ("spmm_layer1_k256", "spmm_layer2_k64")
-    launches_per_step = 4
+
+    @property
+    def launches_per_step(self):
+        # SpMM calls per forward (one per column panel; 2 with one rank, 4 with two, 7 beyond) x
+        # kernels per call (rows kernel, + heavy-segment kernel and its fix-up when the block has heavy rows)
+        calls = 2 if self.world == 1 else (4 + 1 if self.world == 2 else 5 + 2)
+        per_call = 3 if (self.shard.plan is not None and self.shard.plan.segments) else 1
+        return calls * per_call
 
     def _spmm_timed(self, shard, B, out, relu):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -518,12 +525,15 @@ class GcnSharded:
                                           spmm_fn=self._spmm_timed if timed else None)
 
     def step(self, ev=None):
+        if ev is not None:
+            self._timed_steps = getattr(self, "_timed_steps", 0) + 1
         self.out = self._forward(self.X, timed=ev is not None)
 
     def stage_times(self):
+        # a layer is several SpMM launches when it runs in column panels: sum them per step
         l1 = [a.elapsed_time(b) for relu, a, b in self._ev if relu]
         l2 = [a.elapsed_time(b) for relu, a, b in self._ev if not relu]
-        steps = max(1, len(l2))
+        steps = max(1, getattr(self, "_timed_steps", 0))
         return {"spmm_layer1_k256": sum(l1) / steps, "spmm_layer2_k64": sum(l2) / steps}
 
     def e2e_step(self):
