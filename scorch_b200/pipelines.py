@@ -70,6 +70,19 @@ def gcn_forward(pos, crd, val, X, W1, W2, plan: Optional[K.CsrPlan] = None) -> t
     return K.spmm_csr(pos, crd, val, hw, plan=plan)
 
 
+def chunk_bounds(units: int, chunks: int, shrink: bool = True) -> list:
+    """First unit of each chunk (+ ``units`` at the end).  ``shrink``: chunk sizes in the ratio
+    (2c-1) : ... : 5 : 3 : 1 — the last chunk, whose kernels and copy back cannot overlap with
+    anything, is the smallest; otherwise equal chunks.  Chunks may be empty when units < chunks."""
+    weights = [2 * (chunks - c) - 1 if shrink else 1 for c in range(chunks)]
+    acc, bounds = 0, [0]
+    for w in weights:
+        acc += w
+        bounds.append(max(bounds[-1], min(units, round(units * acc / sum(weights)))))
+    bounds[-1] = units
+    return bounds
+
+
 class HostSparseAttention:
     """``sparse_attention`` for operands that live in (pinned) host memory, as the reference's
     callers hold them: the (batch*heads) units are cut into chunks and pipelined over copy and
@@ -88,12 +101,7 @@ class HostSparseAttention:
         self.plan = K.plan_for(pos, crd.numel())
         self.attn_plan = attention_plan(pos, crd, d, d)
         self.block_plan = None if self.attn_plan else attention_block_plan(pos, crd)
-        weights = [2 * (chunks - c) - 1 if shrink else 1 for c in range(chunks)]   # 7, 5, 3, 1
-        acc, self.bounds = 0, [0]
-        for w in weights:
-            acc += w
-            self.bounds.append(max(self.bounds[-1], min(units, round(units * acc / sum(weights)))))
-        self.bounds[-1] = units
+        self.bounds = chunk_bounds(units, chunks, shrink)
         self.dev = [torch.empty((units, seq, d), dtype=torch.float32, device=dev) for _ in range(3)]
         self.scores = (None if self.attn_plan else
                        torch.empty((units, crd.numel()), dtype=torch.float32, device=dev))

@@ -116,3 +116,20 @@ def test_all_ones_mask_check_is_cached_until_the_tensor_is_written():
     v[3] = 1.0
     assert K._mask_is_all_ones(v) is True
     assert K._mask_is_all_ones(torch.full((4,), 1.0 + 1e-6)) is False
+
+
+def test_host_attention_chunk_bounds():
+    """Chunks of the host-tensor attention front end: cover every unit once, in order, shrinking
+    towards the end; degenerate sizes give empty chunks, never a gap."""
+    from scorch_b200.pipelines import chunk_bounds
+    assert chunk_bounds(32, 4) == [0, 14, 24, 30, 32]
+    assert chunk_bounds(32, 4, shrink=False) == [0, 8, 16, 24, 32]
+    for units in (1, 2, 3, 5, 8, 31, 32, 100):
+        for chunks in (1, 2, 3, 4, 8):
+            for shrink in (True, False):
+                b = chunk_bounds(units, chunks, shrink)
+                assert len(b) == chunks + 1 and b[0] == 0 and b[-1] == units
+                assert all(x <= y for x, y in zip(b, b[1:]))
+                sizes = [y - x for x, y in zip(b, b[1:])]
+                if shrink and units >= 4 * chunks:
+                    assert all(x >= y for x, y in zip(sizes, sizes[1:]))
