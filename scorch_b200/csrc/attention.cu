@@ -9,7 +9,8 @@
 //     of the stored columns per row, and
 //   * a CSR list of the remaining entries (the scattered ones).
 // A call then runs three kernels:
-//   1. the gather SDDMM over the remaining entries, scores into a compact scratch array;
+//   1. the gather SDDMM over the remaining entries (columns from the plan's compact copy),
+//      scores into a compact scratch array;
 //   2. attn_block_kernel, one warp per 16 mask rows: for every block of the row block
 //      S = Q K^T on the tensor cores, entries that are not stored masked to -inf, a running
 //      row maximum / sum (started from the scratch scores of the same rows), P = exp(S - max),
@@ -245,16 +246,6 @@ struct AttnArgs {
   float scale;
 };
 
-// One warp per row block.  Thread (g, t) = (lane / 4, lane % 4) owns rows g and g+8 of the row
-// block in every fragment.  Layouts (see mma_tf32.cuh):
-//   S = Q K^T : A = Q rows, B column g of n-tile n = K row 8n+g; the feature index is permuted so
-//               that k-step (4q+h) uses features 32q + 8t + 2h (+1): 256-bit loads of Q and K.
-//               c[n][0..1] = S[g][8n+2t, +1], c[n][2..3] = S[g+8][8n+2t, +1].
-//   O += P V  : k-step n covers block columns 8n..8n+7 with k-slot t = column 8n+2t and k-slot
-//               t+4 = column 8n+2t+1, which is exactly where S left P: no data movement between
-//               the two products.  B of column tile u is V[8n+2t (+1)][g*KT + u] (logical column
-//               (u, g) = actual column g*KT + u), so a thread reads KT contiguous floats per V
-//               row and writes KT contiguous floats per output row.
 // x = hi + lo with both parts valid TF32 values (low 13 mantissa bits zero): hi is x truncated,
 // lo the truncated remainder, so hi*hi + hi*lo + lo*hi misses the product by ~2^-20 relative.
 // (Two logic operations and one subtraction; rounding instead of truncating measured slower
@@ -280,9 +271,20 @@ __device__ __forceinline__ Float8 ldg8(const float* p) {
                : "l"(p));
   return r;
 }
+
+// One warp per row block.  Thread (g, t) = (lane / 4, lane % 4) owns rows g and g+8 of the row
+// block in every fragment.  Layouts (see mma_tf32.cuh):
+//   S = Q K^T : A = Q rows, B column g of n-tile n = K row 8n+g; the feature index is permuted so
+//               that k-step (4q+h) uses features 32q + 8t + 2h (+1): 256-bit loads of Q and K.
+//               c[n][0..1] = S[g][8n+2t, +1], c[n][2..3] = S[g+8][8n+2t, +1].
+//   O += P V  : k-step n covers block columns 8n..8n+7 with k-slot t = column 8n+2t and k-slot
+//               t+4 = column 8n+2t+1, which is exactly where S left P: no data movement between
+//               the two products.  B of column tile u is V[8n+2t (+1)][g*KT + u] (logical column
+//               (u, g) = actual column g*KT + u), so a thread reads KT contiguous floats per V
+//               row and writes KT contiguous floats per output row.
+// Three CTAs per SM (168 registers; four spill, two leave the tensor pipe idle more often).
 constexpr int kAttnWarps = 4;  // row blocks per CTA (1 and 2 measured the same)
 template <int D16>  // head dimension d = 16 * D16 (of Q, K and V)
-// (three CTAs per SM: 168 registers; four spill, two leave the tensor pipe idle more often)
 __global__ void __launch_bounds__(kAttnWarps * 32, 12 / kAttnWarps)
 attn_block_kernel(AttnArgs a) {
   constexpr int KT = 2 * D16;
