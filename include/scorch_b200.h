@@ -286,6 +286,26 @@ SB_API int sb_coo_rows_to_csr_pos(int64_t m, int64_t nnz, const int32_t* row_sor
 SB_API int sb_csr_pos_to_coo_rows(int64_t m, int64_t nnz, const int32_t* pos, int32_t* row,
                                   void* stream);
 
+/* --------------------------------------------------------------------------------------------
+ * More format plumbing, so that whole pipelines stay on the device.
+ *   dense -> CSR : the non-zero entries of a row-major fp32 matrix (what the reference's callers
+ *                  get from torch's to_sparse_csr(), bench/bench_sparse_autoencoder.py:233,261;
+ *                  -0.0 is dropped, NaN kept).  Two calls because the output size is data
+ *                  dependent: _count writes pos[0..m] and returns the number of stored entries
+ *                  (synchronises), the caller allocates crd / val, _fill writes them in ascending
+ *                  column order.  `ws`: sb_dense_to_csr_workspace_bytes(m) bytes.
+ *   sb_csr_sym_normalize_f32 : val[p] = d_i^-1/2 * d_j^-1/2 for the entry p = (i, j) of a square
+ *                  pattern, d = stored entries per row (pattern of A + I; rows without entries
+ *                  give 0).  Replaces: compute_normalized_adj, bench/bench_gcn.py:233-267.
+ * -------------------------------------------------------------------------------------------- */
+SB_API size_t sb_dense_to_csr_workspace_bytes(int64_t m);
+SB_API int sb_dense_to_csr_count(int64_t m, int64_t n, const float* A, int64_t lda, int32_t* pos,
+                                 int64_t* nnz_host, void* ws, size_t ws_bytes, void* stream);
+SB_API int sb_dense_to_csr_fill(int64_t m, int64_t n, const float* A, int64_t lda,
+                                const int32_t* pos, int32_t* crd, float* val, void* stream);
+SB_API int sb_csr_sym_normalize_f32(int64_t m, int64_t nnz, const int32_t* pos, const int32_t* crd,
+                                    float* val, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

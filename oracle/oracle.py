@@ -194,6 +194,29 @@ def spgemm_values_acc64(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n, Cpos, Ccrd):
     return out
 
 
+# ---- format plumbing (numpy) ---------------------------------------------------------------
+def dense_to_csr(A):
+    """Row pointers, columns, values of the non-zero entries of a dense matrix in row-major
+    order: what torch.Tensor.to_sparse_csr() gives the reference's callers
+    (bench/bench_sparse_autoencoder.py:233,261).  -0.0 is dropped, NaN kept."""
+    A = np.asarray(A)
+    keep = A != 0
+    pos = np.concatenate([[0], np.cumsum(keep.sum(axis=1))]).astype(np.int32)
+    crd = np.nonzero(keep)[1].astype(np.int32)
+    return pos, crd, A[keep]
+
+
+def csr_sym_normalize_acc64(pos, crd):
+    """val[p] = d_i^-1/2 d_j^-1/2 with d = stored entries per row (the pattern is A + I):
+    bench/bench_gcn.py:233-267 (degree by scatter-add of ones, deg^-0.5, inf -> 0), in float64."""
+    pos = np.asarray(pos, dtype=np.int64)
+    deg = np.diff(pos).astype(np.float64)
+    with np.errstate(divide="ignore"):
+        dinv = np.where(deg > 0, deg ** -0.5, 0.0)
+    rows = np.repeat(np.arange(len(deg)), np.diff(pos))
+    return dinv[rows] * dinv[np.asarray(crd, dtype=np.int64)]
+
+
 def allclose_report(got, want64, rtol=1e-4, atol=1e-5):
     """(ok, max_abs_err, n_violations) of |got - want| <= atol + rtol*|want| in float64."""
     got = np.asarray(got, dtype=np.float64).ravel()

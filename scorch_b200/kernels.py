@@ -468,3 +468,39 @@ def csr_pos_to_coo_rows(pos: torch.Tensor, nnz: int) -> torch.Tensor:
         check(_lib.lib().sb_csr_pos_to_coo_rows(pos.numel() - 1, nnz, pos.data_ptr(),
                                                 row.data_ptr(), _stream()))
     return row
+
+
+def dense_to_csr(A: torch.Tensor):
+    """(pos, crd, val) of the non-zero entries of a 2-D float32 CUDA matrix, rows and columns
+    ascending — torch's ``to_sparse_csr()`` on the device through the library (the reference's
+    callers convert pruned weight matrices this way, bench/bench_sparse_autoencoder.py:233,261)."""
+    A = _row_major_2d(_dev(A, torch.float32, "A"), "A")
+    if A.dim() != 2:
+        raise ValueError("A must be 2-D")
+    m, n = A.shape
+    L = _lib.lib()
+    pos = torch.empty(m + 1, dtype=torch.int32, device=A.device)
+    wbytes = L.sb_dense_to_csr_workspace_bytes(m)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=A.device)
+    nnz = C.c_int64(0)
+    with torch.cuda.device(A.device):
+        check(L.sb_dense_to_csr_count(m, n, A.data_ptr(), A.stride(0), pos.data_ptr(), C.byref(nnz),
+                                      ws.data_ptr(), wbytes, _stream()))
+        crd = torch.empty(nnz.value, dtype=torch.int32, device=A.device)
+        val = torch.empty(nnz.value, dtype=torch.float32, device=A.device)
+        check(L.sb_dense_to_csr_fill(m, n, A.data_ptr(), A.stride(0), pos.data_ptr(), crd.data_ptr(),
+                                     val.data_ptr(), _stream()))
+    return pos, crd, val
+
+
+def csr_sym_normalize(pos: torch.Tensor, crd: torch.Tensor) -> torch.Tensor:
+    """Values d_i^-1/2 d_j^-1/2 of the symmetric normalisation D^-1/2 (A + I) D^-1/2 for a square
+    CSR pattern that already holds the self-loops; d = stored entries per row
+    (reference: compute_normalized_adj, bench/bench_gcn.py:233-267)."""
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    val = torch.empty(crd.numel(), dtype=torch.float32, device=crd.device)
+    with torch.cuda.device(crd.device):
+        check(_lib.lib().sb_csr_sym_normalize_f32(pos.numel() - 1, crd.numel(), pos.data_ptr(),
+                                                  crd.data_ptr(), val.data_ptr(), _stream()))
+    return val
