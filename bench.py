@@ -49,9 +49,9 @@ NCU_TRAFFIC_BYTES = {
         "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel
     },
     "one attention call": {
-        "sddmm_kernel": 74_784_512,              # scores of the entries outside the blocks
-        "attn_block_kernel": 146_464_256,
-        "spmm_rows_kernel": 96_271_360,          # P V of the entries outside the blocks
+        "sddmm_kernel": 75_042_304,              # scores of the entries outside the blocks
+        "attn_block_kernel": 147_454_720,
+        "spmm_rows_kernel": 95_983_360,          # P V of the entries outside the blocks
     },
 }
 
