@@ -1,26 +1,36 @@
 """Benchmark of the sparse hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c1|c2|c3|c5] [--impl reference]
 
 A "step" is one pass of the hot path over one batch of synthetic input.  The default workload is
-the sparse-attention configuration (SDDMM -> row softmax -> SpMM over 4 x 8 heads, seq 4096,
-head_dim 64, band-128 + 1 % random mask); with N > 1 every rank processes its own batch of the
-same size (independent heads: no data-path collective, weak scaling).
+configuration 4, the largest one that fits a GPU and the one specified at 1/2/4/8 GPUs: a 2-layer
+GCN forward on a 2 M-node power-law graph.  With N > 1 the graph's rows are split over the ranks by
+stored entries and every layer all-gathers its dense features over NCCL inside the timed step
+(strong scaling: the problem is fixed, the ranks share it).
 
 One JSON line is printed by rank 0:
   value      device-resident throughput (inputs already in HBM), GFLOP/s over all ranks
-  e2e        the same step through the public host-tensor API: pinned host inputs -> device,
-             kernels, result -> host, all inside the timed region
+  e2e        the same step from pinned host inputs to a pinned host result, copies inside
   roofline   for the kernel with the largest share of the step: algorithmic bytes per launch /
-             mean launch duration (CUDA events inside the timed region) against the measured
-             HBM copy bandwidth
+             mean launch duration (CUDA events inside the timed region) against the measured HBM
+             copy bandwidth; `gather_model` beside it counts every gathered operand row as traffic
+  phases     mean ms per step of the sharded forward's parts (dense transforms, SpMM launches,
+             all-gathers on the communication stream, main-stream waits for gathered chunks)
+  parity_check  sampled output rows of both sparse products of the timed forward against the
+             float64 CPU oracle (the run exits non-zero when it fails)
+  configs    (one GPU only) the other four configurations, each with its own step time, roofline
+             and CPU baseline
   cpu_baseline  the reference's own OpenMP kernels (oracle/_ref, "reference") or the C port
              ("port") on this machine's host cores, on a bounded sample of the same workload
 `--impl reference` times that CPU path as the whole run and prints the same line shape.
+
+The K timed steps are repeated as blocks until the timed region is at least a second long; the
+reported step time is that of the median block.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -33,27 +43,21 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# The CPU arm uses every host core this process may run on.  Launchers that start one process
+# per GPU export OMP_NUM_THREADS=1; the OpenMP runtime reads the variable when it is first
+# loaded (with torch), so it is corrected here, before that import.
+_HOST_CORES = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+if "reference" in sys.argv[1:]:
+    os.environ["OMP_NUM_THREADS"] = str(_HOST_CORES)
+    os.environ.pop("OMP_PROC_BIND", None)
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 METRIC = "SpMM/SDDMM GFLOP/s"
 UNIT = "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
-
-# DRAM bytes (read + write) per launch of each kernel from ncu captures of this benchmark's
-# default workload, summarised under profiles/.  None = not captured yet.
-NCU_TRAFFIC_BYTES = {
-    "three operators": {
-        "sddmm_kernel": 273_008_640,             # SDDMM stage: block kernel + remainder kernel
-        "csr_row_softmax_kernel": 251_335_936,
-        "spmm_rows_kernel": 319_077_120,         # SpMM stage: block kernel + remainder kernel
-    },
-    "one attention call": {
-        "sddmm_kernel": 75_042_304,              # scores of the entries outside the blocks
-        "attn_block_kernel": 147_454_720,
-        "spmm_rows_kernel": 95_983_360,          # P V of the entries outside the blocks
-    },
-}
+RTOL, ATOL = 1e-4, 1e-5
 
 
 def measured_peaks():
@@ -63,6 +67,33 @@ def measured_peaks():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def ncu_traffic(workload: str, kernel: str):
+    """DRAM bytes (read + write) per launch of `kernel` on `workload` from the profiler capture
+    recorded in profiles/ncu_traffic.json, or None when there is no capture or the kernel's
+    source file has changed since it was taken."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            table = json.load(f)["captures"]
+    except Exception:
+        return None
+    for e in table:
+        if e.get("workload") == workload and e.get("kernel") == kernel:
+            try:
+                with open(os.path.join(ROOT, e["source"]), "rb") as f:
+                    if hashlib.sha256(f.read()).hexdigest() != e["source_sha256"]:
+                        return None
+            except Exception:
+                return None
+            return e.get("dram_bytes_per_launch")
+    return None
+
+
+def host_threads() -> dict:
+    from oracle import oracle as O
+    return {"os_cpu_count": os.cpu_count(), "affinity": _HOST_CORES,
+            "torch_threads": torch.get_num_threads(), "openmp_threads": O.num_threads()}
 
 
 # ---- clocks sampler ------------------------------------------------------------------------------
@@ -97,7 +128,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.out.close()
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         try:
             for line in open(self.path):
@@ -107,6 +138,7 @@ class ClockSampler:
                 try:
                     sm.append(float(parts[1]))
                     mx.append(float(parts[2]))
+                    power.append(float(parts[3]))
                 except ValueError:
                     continue
                 for name, flag in zip(names, parts[5:9]):
@@ -115,13 +147,49 @@ class ClockSampler:
             os.unlink(self.path)
         except Exception:
             pass
-        return {"sm_mhz": statistics.median(sm) if sm else None,
+        # "under load": samples taken while the GPU drew clearly more than its idle power
+        load = [s for s, p in zip(sm, power) if p > 350.0] or sm
+        return {"sm_mhz": statistics.median(load) if load else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "samples_under_load": len(load) if load is not sm else 0}
 
 
 # ---- workloads -----------------------------------------------------------------------------------
-class SparseAttention:
+class Workload:
+    """What the measuring loop needs from a configuration."""
+    name = ""
+    units = 1
+    kernels = ()
+    launches_per_step = 1
+    flush = None
+    h2d_bytes = 0
+    d2h_bytes = 0
+
+    def run_info(self):
+        return {}
+
+    def e2e_step(self):
+        raise NotImplementedError
+
+    def begin_block(self):
+        pass
+
+    def stage_times(self, evs):
+        return {name: statistics.mean(e[j].elapsed_time(e[j + 1]) for e in evs)
+                for j, name in enumerate(self.kernels)}
+
+    def extras(self, stage_ms):
+        return {}
+
+    def release(self):
+        """Drop every tensor the workload holds (the next configuration gets the memory)."""
+        import gc
+        self.__dict__.clear()
+        gc.collect()
+        torch.cuda.empty_cache()
+
+
+class SparseAttention(Workload):
     """Config 2: SDDMM + row softmax + SpMM, (batch*heads) independent units sharing one mask."""
     name = "c2_sparse_attention_seq4096_h8_d64_b4_band128_rand1pct"
 
@@ -130,18 +198,23 @@ class SparseAttention:
         self.window, self.density = window, density
         self.units = batch * heads
 
-    def setup(self, rank: int):
-        from scorch_b200 import kernels as K, workloads as W
-        self.K = K
+    def host_inputs(self, units=None, rank=0):
+        from scorch_b200 import workloads as W
         self.mask = W.attention_mask(self.seq, self.window, self.density, seed=0)
-        Q, Km, V = W.attention_qkv(self.batch, self.heads, self.seq, self.d, seed=1 + rank)
+        self.nnz = self.mask.nnz
+        if units is None:
+            return W.attention_qkv(self.batch, self.heads, self.seq, self.d, seed=1 + rank)
+        return W.attention_qkv(1, units, self.seq, self.d, seed=1 + rank)
+
+    def setup(self, rank: int):
+        from scorch_b200 import kernels as K, pipelines as P
+        self.K = K
+        Q, Km, V = self.host_inputs(rank=rank)
         self.host = [t.pin_memory() for t in (Q, Km, V)]
         self.host_out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32).pin_memory()
         self.pos, self.crd, self.mval = (t.cuda() for t in (self.mask.pos, self.mask.crd, self.mask.val))
         self.Q, self.Km, self.V = (t.cuda() for t in self.host)
-        self.nnz = self.mask.nnz
         self.plan = K.CsrPlan(self.pos, self.nnz)
-        from scorch_b200 import pipelines as P
         no_blocks = bool(os.environ.get("SCORCH_B200_NO_BLOCKS"))
         # the one-call attention path (what pipelines.sparse_attention picks for this mask); the
         # three-operator path is timed instead with SCORCH_B200_NO_FUSED=1
@@ -150,10 +223,11 @@ class SparseAttention:
         self.block_plan = None if no_blocks or self.attn_plan else P.attention_block_plan(self.pos, self.crd)
         if self.attn_plan:
             self.kernels = ("sddmm_kernel", "attn_block_kernel", "spmm_rows_kernel")
+        else:
+            self.kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
         self.scores = (None if self.attn_plan else
                        torch.empty((self.units, self.nnz), dtype=torch.float32, device="cuda"))
         self.out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32, device="cuda")
-        from scorch_b200 import pipelines as P
         self.host_api = P.HostSparseAttention(self.pos, self.crd, self.mval, self.units, self.seq, self.d)
 
     @property
@@ -161,16 +235,15 @@ class SparseAttention:
         return 2 * (2.0 * self.nnz * self.d) * self.units
 
     def config(self):
-        bp = self.attn_plan or self.block_plan
-        scores = 0 if self.attn_plan else self.units * self.nnz * 4
         return {"workload": self.name, "units_per_gpu": self.units, "seq": self.seq, "head_dim": self.d,
-                "mask_nnz": self.nnz,
-                "path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
+                "mask_nnz": self.nnz, "l2": "inputs larger than L2"}
+
+    def run_info(self):
+        bp = self.attn_plan or self.block_plan
+        return {"path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
                          if self.attn_plan else "sddmm, row softmax, spmm"),
                 "blocks_16x16": bp.blocks if bp else 0,
-                "entries_outside_blocks": bp.rem_nnz if bp else self.nnz,
-                "l2": "inputs larger than L2 (Q,K,V,O,scores,mask = "
-                f"{(4 * self.units * self.seq * self.d * 4 + scores + self.nnz * 8) >> 20} MiB)"}
+                "entries_outside_blocks": bp.rem_nnz if bp else self.nnz}
 
     def alg_bytes(self):
         """Algorithmic bytes per launch (each array read once / written once)."""
@@ -195,8 +268,8 @@ class SparseAttention:
             "spmm_rows_kernel": idx + u * (nnz * 4 + 2 * s * d * 4),
         }
 
-    def _run(self, Q, Km, V, ev=None):
-        K = self.K
+    def step(self, ev=None):
+        K, Q, Km, V = self.K, self.Q, self.Km, self.V
         if ev is not None:
             ev[0].record()
         if self.attn_plan:
@@ -219,16 +292,11 @@ class SparseAttention:
         if ev is not None:
             ev[3].record()
 
-    # stage names; with a block plan the SDDMM and SpMM stages are two launches each
-    # (tensor-core kernel over the dense blocks + gather kernel over the remaining entries)
-    kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
-
     @property
     def launches_per_step(self):
-        return 5 if self.block_plan else 3   # (the attention call: 3 kernels)
-
-    def step(self, ev=None):
-        self._run(self.Q, self.Km, self.V, ev)
+        # with a block plan the SDDMM and SpMM stages of the three-operator path are two launches
+        # each (tensor-core kernel over the dense blocks + gather kernel over the other entries)
+        return 5 if self.block_plan else 3
 
     def e2e_step(self):
         # the public host-tensor call: pinned Q, K, V in, pinned O out, copies inside
@@ -242,10 +310,13 @@ class SparseAttention:
     def d2h_bytes(self):
         return self.host_out.numel() * 4
 
+    def traffic_key(self):
+        return self.name + (":one_call" if self.attn_plan else ":three_operators")
+
     # -- CPU reference on a bounded sample ---------------------------------------------------------
     def cpu_sample(self, units: int, repeats: int):
         """`units` heads through the reference's kernels: SDDMM (COO prebuilt, its fastest route),
-        row softmax, SpMM.  Returns (GFLOP/s, description)."""
+        row softmax, SpMM.  Returns (GFLOP/s, kind, seconds, description)."""
         from oracle import oracle as O, ref_loader
         ref = ref_loader.load()
         pos, crd, mval = self.mask.pos, self.mask.crd, self.mask.val
@@ -278,25 +349,28 @@ class SparseAttention:
                                             f"row softmax + spmm_csr_float_v2 ({kind})")
 
 
-class SpmmWorkload:
+class SpmmWorkload(Workload):
     """Configs 1 and 3: one CSR x dense product."""
 
     def __init__(self, which: str):
         self.which = which
         self.name = {"c1": "c1_spmm_4096x4096_1pct_k64", "c3": "c3_sae_decode_8192x32768_top32_k4096"}[which]
-        self.units = 1
 
     def setup(self, rank: int):
         from scorch_b200 import kernels as K, workloads as W
         self.K = K
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
         if self.which == "c1":
             A = W.csr_uniform(4096, 4096, 0.01, seed=0)
             B = W.dense_normal(4096, 64, seed=1)
         else:
-            A = W.sae_activations(8192, 32768, 32, seed=0, device="cuda").to("cpu")
-            B = W.sae_decoder(32768, 4096, seed=1, device="cuda").cpu()
+            A = W.sae_activations(8192, 32768, 32, seed=0, device=dev).to("cpu")
+            B = W.sae_decoder(32768, 4096, seed=1, device=dev).cpu()
         self.A = A
         self.m, self.n, self.k, self.nnz = A.shape[0], A.shape[1], B.shape[1], A.nnz
+        self.host = [A.val, B]
+        if dev == "cpu":
+            return
         self.host = [A.val.pin_memory(), B.pin_memory()]
         self.pos, self.crd = A.pos.cuda(), A.crd.cuda()
         self.val, self.B = (t.cuda() for t in self.host)
@@ -313,14 +387,13 @@ class SpmmWorkload:
 
     def config(self):
         return {"workload": self.name, "m": self.m, "n": self.n, "k": self.k, "nnz": self.nnz,
-                "l2": "L2 flushed by a 256 MiB write between iterations" if self.flush is not None
+                "l2": "L2 flushed by a 256 MiB write between iterations" if self.which == "c1"
                 else "inputs larger than L2"}
 
     def alg_bytes(self):
         return {"spmm_rows_kernel": (self.m + 1) * 4 + self.nnz * 8 + self.n * self.k * 4 + self.m * self.k * 4}
 
     kernels = ("spmm_rows_kernel",)
-    launches_per_step = 1
 
     def step(self, ev=None):
         if self.flush is not None:
@@ -330,6 +403,12 @@ class SpmmWorkload:
         self.K.spmm_csr(self.pos, self.crd, self.val, self.B, plan=self.plan, out=self.out)
         if ev is not None:
             ev[1].record()
+
+    def extras(self, stage_ms):
+        ms = stage_ms["spmm_rows_kernel"]
+        return {"gather_model": {"bytes": self.nnz * (8 + self.k * 4) + self.m * self.k * 4,
+                                 "GBps": (self.nnz * (8 + self.k * 4) + self.m * self.k * 4) / (ms * 1e-3) / 1e9,
+                                 "what": "every stored entry counted as one operand-row read"}}
 
     def e2e_step(self):
         for dst, src in zip(self.stage, self.host):
@@ -344,7 +423,10 @@ class SpmmWorkload:
 
     @property
     def d2h_bytes(self):
-        return self.host_out.numel() * 4
+        return self.m * self.k * 4
+
+    def traffic_key(self):
+        return self.name
 
     def cpu_sample(self, units: int, repeats: int):
         from oracle import oracle as O, ref_loader
@@ -366,14 +448,14 @@ class SpmmWorkload:
         return self.flops_per_step / dt / 1e9, kind, dt, f"the whole product, spmm_csr_float_v2 ({kind})"
 
 
-class SpgemmSpmv:
+class SpgemmSpmv(Workload):
     """Config 5: SpMV sweep and SpGEMM C = A A on a 2M power-law matrix; symbolic and numeric
     phases timed separately.  Metric here: products (2 flops each) + SpMV flops per second."""
     name = "c5_spmspm_spmv_2M_powerlaw"
+    SPMV_SWEEP = 10  # back-to-back SpMV calls per step: keeps the GPU busy between launches
 
     def __init__(self, n=2_000_000):
         self.n = n
-        self.units = 1
 
     def setup(self, rank: int):
         from scorch_b200 import kernels as K, workloads as W
@@ -385,7 +467,7 @@ class SpgemmSpmv:
         self.plan = K.CsrPlan(A.pos, self.nnz)
         lens = (A.pos[1:] - A.pos[:-1]).long()
         self.products = int(lens[A.crd.long()].sum().item())
-        self.timings = {}
+        self.timings = []
 
     @property
     def flops_per_step(self):
@@ -393,8 +475,10 @@ class SpgemmSpmv:
 
     def config(self):
         return {"workload": self.name, "n": self.n, "nnz": self.nnz, "products": self.products,
-                "spmv_calls_per_step": self.SPMV_SWEEP,
-                "l2": "inputs larger than L2"}
+                "spmv_calls_per_step": self.SPMV_SWEEP, "l2": "inputs larger than L2"}
+
+    def run_info(self):
+        return {"nnz_C": getattr(self, "nnzc", None)}
 
     def alg_bytes(self):
         n, nnz = self.n, self.nnz
@@ -406,7 +490,8 @@ class SpgemmSpmv:
     kernels = ("spmv", "spgemm_symbolic", "spgemm_numeric")
     launches_per_step = 12
 
-    SPMV_SWEEP = 10  # back-to-back SpMV calls per step: keeps the GPU busy between launches
+    def begin_block(self):
+        self.timings = []
 
     def step(self, ev=None):
         A = self.A
@@ -419,20 +504,26 @@ class SpgemmSpmv:
         t = {}
         cpos, ccrd, cval = self.K.spgemm_csr(A.pos, A.crd, A.val, A.pos, A.crd, A.val, self.n, timings=t)
         self.nnzc = int(ccrd.numel())
-        self.timings = t
+        if ev is not None:
+            self.timings.append(t)
         del cpos, ccrd, cval
 
-    def e2e_step(self):
-        raise NotImplementedError
+    def stage_times(self, evs):
+        return {"spmv": statistics.mean(e[0].elapsed_time(e[1]) for e in evs) / self.SPMV_SWEEP,
+                "spgemm_symbolic": statistics.mean(t["symbolic_ms"] for t in self.timings),
+                "spgemm_numeric": statistics.mean(t["numeric_ms"] for t in self.timings)}
 
-    h2d_bytes = 0
-    d2h_bytes = 0
+    def extras(self, stage_ms):
+        return {"products_per_second": self.products / (stage_ms["spgemm_numeric"] * 1e-3)}
+
+    def traffic_key(self):
+        return self.name
 
     def cpu_sample(self, units: int, repeats: int):
         from oracle import oracle as O, ref_loader
         ref = ref_loader.load()
-        # bounded sample: the first 100k rows of A against the whole A
-        rows = min(self.n, 100_000)
+        # bounded sample: the first rows of A against the whole A
+        rows = min(self.n, 50_000)
         pos = self.A.pos[: rows + 1].cpu()
         e = int(pos[-1])
         crd, val = self.A.crd[:e].cpu(), self.A.val[:e].cpu()
@@ -450,95 +541,121 @@ class SpgemmSpmv:
         return 2.0 * prods / dt / 1e9, kind, dt, f"SpGEMM of the first {rows} rows of A with A ({kind})"
 
 
-class GcnSharded:
+class GcnSharded(Workload):
     """Config 4: 2-layer GCN forward on a 2M-node power-law graph, rows sharded by nnz over the
-    ranks; per layer the dense features are all-gathered (NCCL) panel by panel, overlapped with
-    the SpMM of earlier panels.  Strong scaling: the graph is fixed, ranks split it."""
-    name = "c4_gcn_2M_powerlaw_k256_k64"
+    ranks; per layer the dense features are all-gathered (NCCL) in row chunks, each overlapped
+    with the SpMM over the chunks that have arrived.  Strong scaling: the graph is fixed, the
+    ranks split it."""
+    K1, K2 = 256, 64
+    CPU_SAMPLE_ROWS = 100_000
 
     def __init__(self, n=2_000_000, world=1):
         self.n, self.world = n, world
-        self.units = 1
+        self.name = ("c4_gcn_2M_powerlaw_k256_k64" if n == 2_000_000
+                     else f"c4_gcn_{n}_nodes_powerlaw_k256_k64")
+
+    # -- inputs ------------------------------------------------------------------------------------
+    def graph(self):
+        from scorch_b200 import workloads as W
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        g = W.gcn_graph(self.n, seed=0, device=dev)
+        self.nnz_global = g.nnz
+        self.max_row = int((g.pos[1:] - g.pos[:-1]).max().item())
+        return g
+
+    def weights(self, dev):
+        from scorch_b200 import workloads as W
+        return W.glorot(self.K1, self.K1, seed=0, device=dev), W.glorot(self.K1, self.K2, seed=1, device=dev)
+
+    def take_cpu_sample_rows(self, g):
+        ns = min(self.CPU_SAMPLE_ROWS, self.n)
+        e = int(g.pos[ns])
+        self.sample = (g.pos[:ns + 1].cpu(), g.crd[:e].cpu(), g.val[:e].cpu())
 
     def setup(self, rank: int):
-        from scorch_b200 import kernels as K, sharded as S, workloads as W
+        from scorch_b200 import sharded as S
         self.S = S
-        g = W.gcn_graph(self.n, seed=0, device="cuda")
-        self.nnz_global = g.nnz
+        self.rank = rank
+        g = self.graph()
         self.shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, self.world)
-        self.max_row = int((g.pos[1:] - g.pos[:-1]).max().item())
         r0, r1 = self.shard.bounds[rank], self.shard.bounds[rank + 1]
-        if rank == 0:
-            ns = min(100_000, self.n)
-            self.sample = (g.pos[:ns + 1].cpu(), g.crd[:int(g.pos[ns])].cpu(), g.val[:int(g.pos[ns])].cpu())
+        if rank == 0 and self.world == 1:
+            self.take_cpu_sample_rows(g)
         del g
         torch.cuda.empty_cache()
         gen = torch.Generator(device="cuda").manual_seed(1)
-        X = torch.randn((self.n, 256), generator=gen, device="cuda", dtype=torch.float32)
+        X = torch.randn((self.n, self.K1), generator=gen, device="cuda", dtype=torch.float32)
         self.X = X[r0:r1].contiguous()
         del X
         torch.cuda.empty_cache()
-        self.W1, self.W2 = W.glorot(256, 256, seed=0, device="cuda"), W.glorot(256, 64, seed=1, device="cuda")
-        self.panel = None if self.world == 1 else "32,32,64,... (layer 1), 32,32 (layer 2)"
+        self.W1, self.W2 = self.weights("cuda")
         self.host_x = self.X.cpu().pin_memory()
         self.stage_x = torch.empty_like(self.X)
-        self.host_out = torch.empty((self.X.shape[0], 64), dtype=torch.float32).pin_memory()
-        self.spmm_ms = []
-        self._ev = []
+        self.host_out = torch.empty((self.X.shape[0], self.K2), dtype=torch.float32).pin_memory()
+        self.timeline = None
 
     @property
     def flops_per_step(self):  # the two sparse products (2*nnz*k); per-rank share is 1/world
-        return 2.0 * self.nnz_global * (256 + 64) / self.world
+        return 2.0 * self.nnz_global * (self.K1 + self.K2) / self.world
 
     def config(self):
         return {"workload": self.name, "nodes": self.n, "nnz": self.nnz_global, "max_row_nnz": self.max_row,
-                "rows_this_rank": self.shard.rows, "heavy_segments_this_rank": self.shard.plan.segments
-                if self.shard.plan else None, "panel": self.panel or "full width",
-                "parallelism": f"row-sharded x{self.world}, all-gather per layer",
-                "flops_counted": "2*nnz*(256+64), the two sparse products; dense X*W GEMMs run inside "
-                                 "the timed step but are not counted", "l2": "inputs larger than L2"}
+                "layers": "H = relu(A (X W1)), out = A (H W2); X 256 wide, W1 256x256, W2 256x64",
+                "parallelism": f"rows sharded by stored entries over {self.world} GPU(s), "
+                               "all-gather of the dense features per layer",
+                "flops_counted": "2*nnz*(256+64), the two sparse products; the dense X*W products run "
+                                 "inside the timed step but are not counted",
+                "l2": "inputs larger than L2"}
+
+    def run_info(self):
+        segs = [b.plan.segments if b.plan is not None else None for b in self.shard.blocks]
+        return {"rows_this_rank": self.shard.rows, "nnz_this_rank": self.shard.nnz,
+                "row_chunks_per_layer": self.shard.chunks, "chunk_rows": self.shard.chunk_rows,
+                "heavy_segments_per_chunk": segs}
 
     def alg_bytes(self):
         rows, nnz, n = self.shard.rows, self.shard.nnz, self.n
         per = lambda k: (rows + 1) * 4 + nnz * 8 + n * k * 4 + rows * k * 4
-        return {"spmm_layer1_k256": per(256), "spmm_layer2_k64": per(64)}
+        return {"spmm_layer1_k256": per(self.K1), "spmm_layer2_k64": per(self.K2)}
 
     kernels = ("spmm_layer1_k256", "spmm_layer2_k64")
 
     @property
     def launches_per_step(self):
-        # SpMM calls per forward (one per column panel; 2 with one rank, 4 with two, 7 beyond) x
-        # kernels per call (rows kernel, + heavy-segment kernel and its fix-up when the block has heavy rows)
-        calls = 2 if self.world == 1 else (4 + 1 if self.world == 2 else 5 + 2)
-        per_call = 3 if (self.shard.plan is not None and self.shard.plan.segments) else 1
-        return calls * per_call
+        # per layer one SpMM call per row chunk; a call is the rows kernel, plus the heavy-segment
+        # kernel and its fix-up when the chunk's sub-matrix has heavy rows
+        per_layer = sum(3 if (b.plan is not None and b.plan.segments) else 1 for b in self.shard.blocks)
+        return 2 * per_layer
 
-    def _spmm_timed(self, shard, B, out, relu):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        self.S._default_spmm(shard, B, out, relu)
-        b.record()
-        self._ev.append((relu, a, b))
-
-    def _forward(self, x, timed=False):
-        return self.S.gcn_forward_sharded(self.shard, x, self.W1, self.W2,
-                                          spmm_fn=self._spmm_timed if timed else None)
+    def begin_block(self):
+        self.timeline = self.S.Timeline()
 
     def step(self, ev=None):
-        if ev is not None:
-            self._timed_steps = getattr(self, "_timed_steps", 0) + 1
-        self.out = self._forward(self.X, timed=ev is not None)
+        self.out = self.S.gcn_forward_sharded(self.shard, self.X, self.W1, self.W2,
+                                              timeline=self.timeline if ev is not None else None)
 
-    def stage_times(self):
-        # a layer is several SpMM launches when it runs in column panels: sum them per step
-        l1 = [a.elapsed_time(b) for relu, a, b in self._ev if relu]
-        l2 = [a.elapsed_time(b) for relu, a, b in self._ev if not relu]
-        steps = max(1, getattr(self, "_timed_steps", 0))
-        return {"spmm_layer1_k256": sum(l1) / steps, "spmm_layer2_k64": sum(l2) / steps}
+    def stage_times(self, evs):
+        self.phases = self.timeline.summary()
+        return {"spmm_layer1_k256": self.phases.get("spmm_layer1", 0.0),
+                "spmm_layer2_k64": self.phases.get("spmm_layer2", 0.0)}
+
+    def extras(self, stage_ms):
+        nnz, rows = self.shard.nnz, self.shard.rows
+        gm = {}
+        for name, k in (("spmm_layer1_k256", self.K1), ("spmm_layer2_k64", self.K2)):
+            b = nnz * (8 + 4 * k) + rows * k * 4
+            gm[name] = {"bytes": b, "GBps": b / (stage_ms[name] * 1e-3) / 1e9 if stage_ms[name] else None}
+        return {"gather_model": {"what": "every stored entry counted as one operand-row read "
+                                         "(no reuse in cache); diagnostic, not the roofline numerator",
+                                 **gm},
+                "phases": {"ms_per_step": self.phases,
+                           "what": "spmm_*, dense_transform and wait_for_gather are spans on the main "
+                                   "stream (wait_for_gather = communication the pipeline did not hide); "
+                                   "all_gather spans run on the communication stream"}}
 
     def e2e_step(self):
         self.stage_x.copy_(self.host_x, non_blocking=True)
-        out = self._forward(self.stage_x)
+        out = self.S.gcn_forward_sharded(self.shard, self.stage_x, self.W1, self.W2)
         self.host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -550,21 +667,93 @@ class GcnSharded:
     def d2h_bytes(self):
         return self.host_out.numel() * 4
 
+    def traffic_key(self):
+        return self.name
+
+    # -- parity of the timed forward ---------------------------------------------------------------
+    def parity_check(self, reduce_max, reduce_sum, rows_total: int = 200):
+        """Sampled rows (evenly spaced + this rank's longest) of both sparse products of the
+        forward that was just timed, against the float64 oracle fed with the dense operand the
+        GPU produced (the X W products are library GEMMs, outside the sparse path)."""
+        from oracle import oracle as O
+        S, shard = self.S, self.shard
+        out = S.gcn_forward_sharded(shard, self.X, self.W1, self.W2)
+        H = shard.buffer("hidden", (shard.rows, self.K1), self.X.device)
+        loc = shard.local
+        lens = (loc.pos[1:] - loc.pos[:-1]).long()
+        per_rank = max(2, rows_total // self.world)
+        rows = torch.unique(torch.cat([
+            torch.linspace(0, shard.rows - 1, per_rank - 1, device=lens.device).long(),
+            lens.argmax().reshape(1)]))
+        starts, cnt = loc.pos[rows].long(), lens[rows]
+        spos = torch.zeros(rows.numel() + 1, dtype=torch.int64, device=lens.device)
+        spos[1:] = torch.cumsum(cnt, 0)
+        idx = torch.repeat_interleave(starts - spos[:-1], cnt) + torch.arange(int(spos[-1]), device=lens.device)
+        cols, inv = torch.unique(loc.crd[idx].long(), return_inverse=True)
+        sval = loc.val[idx]
+        worst, bad, checked = 0.0, 0, 0
+        for operand_local, result, relu in ((torch.matmul(self.X, self.W1), H, True),
+                                            (torch.matmul(H, self.W2), out, False)):
+            full = S.gather_rows(shard, operand_local)
+            sub = full[cols].cpu().numpy()
+            del full
+            want = O.spmm_csr_acc64(spos.to(torch.int32).cpu().numpy(), inv.to(torch.int32).cpu().numpy(),
+                                    sval.cpu().numpy(), sub, None, relu)
+            ok, err, nbad = O.allclose_report(result[rows].cpu().numpy(), want, RTOL, ATOL)
+            worst, bad, checked = max(worst, float(err)), bad + int(nbad), checked + rows.numel()
+        worst, bad, checked = reduce_max(worst), int(reduce_sum(bad)), int(reduce_sum(checked))
+        return {"rows": checked, "max_abs_err": worst, "elements_outside_tolerance": bad, "ok": bad == 0,
+                "tolerance": f"rtol {RTOL} / atol {ATOL} against float64 accumulation, per sparse product",
+                "what": "rows of relu(A (X W1)) and of A (H W2) on every rank, longest row included"}
+
+    # -- CPU reference on a bounded sample ---------------------------------------------------------
+    def cpu_prepare(self):
+        """Host operands of the CPU sample, allocated once outside any timed call."""
+        pos, crd, val = self.sample
+        rows = pos.numel() - 1
+        gen = torch.Generator().manual_seed(2)
+        self.cpu_ops = {
+            "Xs": torch.randn((rows, self.K1), generator=gen, dtype=torch.float32),
+            "T1": torch.randn((self.n, self.K1), generator=gen, dtype=torch.float32),
+            "T2": torch.randn((self.n, self.K2), generator=gen, dtype=torch.float32),
+            "W": self.weights("cpu"),
+        }
+
     def cpu_sample(self, units: int, repeats: int):
+        """The sample rows' share of one forward on the host: their dense transforms (torch) and
+        both sparse products (the reference's spmm_csr_float_v2) against full-height operands."""
         from oracle import oracle as O, ref_loader
         ref = ref_loader.load()
+        if not hasattr(self, "cpu_ops"):
+            self.cpu_prepare()
         pos, crd, val = self.sample
-        rows, n, k = pos.numel() - 1, self.n, 256
-        B = torch.randn((n, k), dtype=torch.float32)
+        rows, n, ops = pos.numel() - 1, self.n, self.cpu_ops
+        W1, W2 = ops["W"]
+
+        def spmm(B, k):
+            if ref is not None:
+                r = ref.spmm_csr_float_v2([rows, k], [rows, n], [[], [pos, crd]], val, [n, k], [[], []],
+                                          B.reshape(-1), 256)
+                return r.storage.value.view(rows, k)
+            return torch.from_numpy(O.spmm_csr_v2(pos.numpy(), crd.numpy(), val.numpy(), B.numpy()))
+
+        def one():
+            torch.matmul(ops["Xs"], W1)
+            h = torch.relu_(spmm(ops["T1"], self.K1))
+            torch.matmul(h, W2)
+            spmm(ops["T2"], self.K2)
+
+        one()  # warm-up: thread start-up and first touch stay outside the timed calls
         t0 = time.perf_counter()
-        if ref is not None:
-            ref.spmm_csr_float_v2([rows, k], [rows, n], [[], [pos, crd]], val, [n, k], [[], []], B.reshape(-1), 256)
-        else:
-            O.spmm_csr_v2(pos.numpy(), crd.numpy(), val.numpy(), B.numpy())
-        dt = time.perf_counter() - t0
+        for _ in range(repeats):
+            one()
+        dt = (time.perf_counter() - t0) / repeats
         kind = "reference" if ref is not None else "port"
-        return 2.0 * crd.numel() * k / dt / 1e9, kind, dt, (f"layer-1 SpMM (k=256) of the first {rows} rows "
-                                                           f"({crd.numel()} entries), spmm_csr_float_v2 ({kind})")
+        flops = 2.0 * crd.numel() * (self.K1 + self.K2)
+        return flops / dt / 1e9, kind, dt, (
+            f"the first {rows} rows' share of one forward ({crd.numel()} stored entries): X W1, "
+            f"spmm_csr_float_v2 k=256 + relu, H W2, spmm_csr_float_v2 k=64 ({kind}); operands "
+            f"are full height ({n} rows)")
 
 
 def make_workload(name: str, world: int = 1, c4_nodes: int = 2_000_000):
@@ -579,40 +768,110 @@ def make_workload(name: str, world: int = 1, c4_nodes: int = 2_000_000):
     raise SystemExit(f"unknown workload {name}")
 
 
+# ---- measuring loop ----------------------------------------------------------------------------------
+def measure(wl, K: int, W: int, world: int, barrier, max_over_ranks, min_seconds: float, max_blocks: int):
+    """W warm-up steps, then blocks of exactly K steps (two events around each block, per-kernel
+    events inside) until the blocks add up to `min_seconds`; returns the median block."""
+    for _ in range(W):
+        wl.step()
+    nk = len(wl.kernels)
+    blocks, total = [], 0.0
+    while True:
+        wl.begin_block()
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nk + 1)] for _ in range(K)]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(K):
+            wl.step(evs[i])
+        end.record()
+        barrier()
+        block_ms = max_over_ranks(start.elapsed_time(end))
+        total += block_ms
+        if wl.flush is not None:
+            # the L2 flush write sits between the per-kernel events, outside them
+            block_ms = max_over_ranks(sum(e[0].elapsed_time(e[-1]) for e in evs))
+        blocks.append((block_ms / K, wl.stage_times(evs)))
+        if total >= min_seconds * 1e3 or len(blocks) >= max_blocks:
+            break
+    order = sorted(range(len(blocks)), key=lambda i: blocks[i][0])
+    step_ms, stage_ms = blocks[order[len(order) // 2]]
+    return step_ms, stage_ms, len(blocks), [b[0] for b in blocks]
+
+
+def measure_e2e(wl, K: int, world: int, barrier, max_over_ranks):
+    try:
+        for _ in range(2):
+            wl.e2e_step()
+    except NotImplementedError:
+        return None
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(K):
+        wl.e2e_step()
+    b.record()
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b)) / K
+    return {"value": wl.flops_per_step * world / (ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms,
+            "steps": K, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes}
+
+
+def roofline_of(wl, stage_ms):
+    peak, peak_kind = measured_peaks()
+    alg = wl.alg_bytes()
+    dom = max((k for k in stage_ms if stage_ms[k]), key=lambda k: stage_ms[k])
+    achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_kind,
+            "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBps": achieved / 8000.0,
+            "algorithmic_bytes_per_launch": alg[dom], "launch_ms": stage_ms[dom],
+            "traffic": ncu_traffic(wl.traffic_key(), dom),
+            "per_kernel": {k: {"ms": stage_ms[k], "algorithmic_GBps": (alg[k] / (stage_ms[k] * 1e-3) / 1e9)
+                               if stage_ms[k] else None} for k in stage_ms}}
+
+
+def cpu_baseline_of(wl, units: int, repeats: int):
+    v, kind, dt, sample = wl.cpu_sample(units, repeats)
+    return {"value": v, "unit": UNIT, "cores": host_threads()["openmp_threads"], "kind": kind,
+            "sample": sample, "seconds_per_sample": dt, "threads": host_threads()}
+
+
 # ---- reference arm --------------------------------------------------------------------------------
 def run_reference(args, rank: int, emit):
+    """The reference's CPU kernels as the whole run: every step is the bounded sample of the
+    workload that `cpu_sample` describes, on all host cores."""
     if rank != 0:
         return
-    wl = make_workload(args.workload, 1, args.c4_nodes)
+    torch.set_num_threads(_HOST_CORES)
+    wl = make_workload(args.workload, args.gpus, args.c4_nodes)
+    sample_units = 1
     if args.workload == "c2":
-        # build host inputs only (no CUDA needed for this arm)
-        from scorch_b200 import workloads as W
-        wl.mask = W.attention_mask(wl.seq, wl.window, wl.density, seed=0)
-        wl.nnz = wl.mask.nnz
         sample_units = 2
-        Q, Km, V = W.attention_qkv(1, sample_units, wl.seq, wl.d, seed=1)
-        wl.host = [Q, Km, V]
-        cfg = {"workload": wl.name, "units_per_gpu": wl.units, "seq": wl.seq, "head_dim": wl.d,
-               "mask_nnz": wl.nnz}
+        wl.host = list(wl.host_inputs(units=sample_units))
+    elif args.workload == "c4":
+        g = wl.graph()
+        wl.take_cpu_sample_rows(g)
+        del g
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        wl.cpu_prepare()
     else:
         wl.setup(0)
-        sample_units = 1
-        cfg = wl.config()
-    for _ in range(max(1, args.warmup) - 1):
+    for _ in range(max(0, args.warmup - 1)):   # (every sample call warms up once itself)
         wl.cpu_sample(sample_units, 1)
     vals, dts = [], []
     for _ in range(args.steps):
         v, kind, dt, sample = wl.cpu_sample(sample_units, 1)
         vals.append(v)
         dts.append(dt)
-    from oracle import oracle as O
     value = statistics.median(vals)
-    cores = max(torch.get_num_threads(), O.num_threads())
+    threads = host_threads()
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.median(dts) * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": cfg,
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "higher_is_better": True, "scaling": "strong" if args.workload == "c4" else "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads["openmp_threads"], "kind": kind,
+                             "sample": sample, "threads": threads},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     emit(line)
@@ -638,12 +897,16 @@ def _bind_to_gpu_numa_node(index: int) -> None:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--workload", default="c4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-units", type=int, default=2, help="heads in the CPU-baseline sample")
+    ap.add_argument("--cpu-units", type=int, default=2, help="heads in the CPU-baseline sample of c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the other four configurations in the one-GPU line")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="repeat the block of K timed steps until the timed region is this long")
     ap.add_argument("--c4-nodes", type=int, default=2_000_000,
                     help="graph size of workload c4 (smaller graphs are for profiler captures)")
     args = ap.parse_args()
@@ -679,98 +942,77 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x: float) -> float:
+    def reduce(x: float, op) -> float:
         if world == 1:
             return x
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=op)
         return float(t.item())
+
+    max_over_ranks = lambda x: reduce(x, dist.ReduceOp.MAX)
+    sum_over_ranks = lambda x: reduce(x, dist.ReduceOp.SUM)
 
     wl = make_workload(args.workload, world, args.c4_nodes)
     wl.setup(rank)
     K, W_ = args.steps, args.warmup
 
-    for _ in range(W_):
-        wl.step()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-
-    # device-resident arm: K steps between two events; per-kernel events inside the region
-    nk = len(wl.kernels)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nk + 1)] for _ in range(K)]
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(K):
-        wl.step(evs[i])
-    end.record()
-    barrier()
-    total_ms = max_over_ranks(start.elapsed_time(end))
-    flush_ms = 0.0
-    if getattr(wl, "flush", None) is not None:
-        # the L2 flush write sits between the per-kernel events, outside them: take it out of the step time
-        flush_ms = total_ms - sum(e[0].elapsed_time(e[-1]) for e in evs)
-    step_ms = (total_ms - flush_ms) / K
-    stage_ms = {}
-    if args.workload == "c4":
-        stage_ms = wl.stage_times()
-    elif args.workload == "c5":
-        stage_ms = {"spmv": statistics.mean(e[0].elapsed_time(e[1]) for e in evs) / wl.SPMV_SWEEP,
-                    "spgemm_symbolic": wl.timings.get("symbolic_ms"), "spgemm_numeric": wl.timings.get("numeric_ms")}
-    else:
-        for j, name in enumerate(wl.kernels):
-            stage_ms[name] = statistics.mean(e[j].elapsed_time(e[j + 1]) for e in evs)
+    step_ms, stage_ms, nblocks, block_ms = measure(wl, K, W_, world, barrier, max_over_ranks,
+                                                   args.min_seconds, 50)
     value = wl.flops_per_step * world / (step_ms * 1e-3) / 1e9
     scaling = "strong" if args.workload == "c4" else "weak"
-
-    # end-to-end arm through host tensors
-    e2e = None
-    try:
-        for _ in range(2):
-            wl.e2e_step()
-        barrier()
-        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_start.record()
-        for _ in range(K):
-            wl.e2e_step()
-        t_end.record()
-        barrier()
-        e2e_ms = max_over_ranks(t_start.elapsed_time(t_end)) / K
-        e2e = {"value": wl.flops_per_step * world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
-               "ms_per_step": e2e_ms, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes}
-    except NotImplementedError:
-        e2e = None
+    e2e = measure_e2e(wl, min(K, 10) if args.workload == "c4" else K, world, barrier, max_over_ranks)
     clocks = sampler.stop() if rank == 0 else None
 
-    peak, peak_kind = measured_peaks()
-    alg = wl.alg_bytes()
-    dom = max((k for k in stage_ms if stage_ms[k]), key=lambda k: stage_ms[k])
-    achieved = alg[dom] / (stage_ms[dom] * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_kind,
-                "unit": "GB/s", "frac": achieved / peak, "algorithmic_bytes_per_launch": alg[dom],
-                "launch_ms": stage_ms[dom],
-                "traffic": (NCU_TRAFFIC_BYTES["one attention call" if wl.attn_plan else "three operators"].get(dom)
-                            if args.workload == "c2" else None),
-                "per_kernel": {k: {"ms": stage_ms[k], "algorithmic_GBps": (alg[k] / (stage_ms[k] * 1e-3) / 1e9)
-                                   if stage_ms[k] else None} for k in stage_ms}}
+    roofline = roofline_of(wl, stage_ms)
+    extras = wl.extras(stage_ms)
+    parity = None
+    if hasattr(wl, "parity_check"):
+        parity = wl.parity_check(max_over_ranks, sum_over_ranks)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle import oracle as O
-        v, kind, dt, sample = wl.cpu_sample(args.cpu_units, 3 if args.workload == "c2" else 1)
-        cpu_baseline = {"value": v, "unit": UNIT, "cores": max(torch.get_num_threads(), O.num_threads()),
-                        "kind": kind, "sample": sample, "seconds_per_sample": dt}
+        cpu_baseline = cpu_baseline_of(wl, args.cpu_units, 3 if args.workload in ("c1", "c2") else 1)
 
+    line = None
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W_,
                 "ms_per_step": step_ms, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic", "config": wl.config(), "e2e": e2e,
-                "gpu_launches": K * wl.launches_per_step, "roofline": roofline, "cpu_baseline": cpu_baseline,
-                "clocks": clocks}
+                "dtype": "f32", "data": "synthetic", "config": wl.config(), "run": wl.run_info(),
+                "timed_blocks": {"blocks_of_K_steps": nblocks, "ms_per_step_each": block_ms,
+                                 "reported": "median block"},
+                "e2e": e2e, "gpu_launches": nblocks * K * wl.launches_per_step, "roofline": roofline,
+                **extras, "parity_check": parity, "cpu_baseline": cpu_baseline, "clocks": clocks}
+
+    # the other four configurations, one GPU only: each with its own step time, roofline, CPU arm
+    if rank == 0 and world == 1 and args.workload == "c4" and not args.no_configs:
+        wl.release()
+        del wl
+        configs = {}
+        for name in ("c1", "c2", "c3", "c5"):
+            w2 = make_workload(name)
+            w2.setup(0)
+            k2 = K if name != "c5" else min(K, 3)
+            ms, st, nb, _ = measure(w2, k2, 3, 1, barrier, max_over_ranks, 0.3, 20)
+            entry = {"config": w2.config(), "run": w2.run_info(), "ms_per_step": ms, "steps": k2, "blocks": nb,
+                     "value": w2.flops_per_step / (ms * 1e-3) / 1e9, "unit": UNIT,
+                     "roofline": roofline_of(w2, st), **w2.extras(st),
+                     "e2e": measure_e2e(w2, min(k2, 10), 1, barrier, max_over_ranks)}
+            if not args.no_cpu_baseline:
+                entry["cpu_baseline"] = cpu_baseline_of(w2, args.cpu_units, 3 if name in ("c1", "c2") else 1)
+            configs[name] = entry
+            w2.release()
+            del w2
+        line["configs"] = configs
+
+    if rank == 0:
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit("parity check of the timed forward failed: " + json.dumps(parity))
 
 
 if __name__ == "__main__":

@@ -103,6 +103,19 @@ SB_API int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const i
                            const void* plan, int64_t plan_segments, void* scratch,
                            size_t scratch_bytes, void* stream);
 
+/* Accumulating form:  C[i, 0:k] = act( bias + C[i, 0:k] + sum_p ... ), same arguments.  A product
+ * whose dense operand arrives in pieces (row chunks of B, each with the matrix entries whose
+ * columns fall in it) is the first piece through sb_spmm_csr_f32 and the others through this
+ * call, bias / ReLU on the last one only.  Vector layout only (SB_ERR_UNSUPPORTED otherwise).
+ * Replaces: the same loops as sb_spmm_csr_f32; spmm_csr_typed (csrc/spmm.h:117-139) and the
+ *           compiler-emitted loop accumulate straight into the output array in the same way. */
+SB_API int sb_spmm_csr_acc_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                               const int32_t* crd, const float* val, const float* B, int64_t ldb,
+                               const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
+                               int64_t stride_val, int64_t stride_b, int64_t stride_c,
+                               const void* plan, int64_t plan_segments, void* scratch,
+                               size_t scratch_bytes, void* stream);
+
 /* Same product for the other registry dtypes (SB_F64, SB_I32, SB_I64; SB_F32 also accepted).
  * Integer products wrap like the reference's C++ arithmetic.
  * Replaces: prebuilt_spmm_csr_{f64,i32,i64}, spmm_csr_double (csrc/ops.cpp:91-116). */

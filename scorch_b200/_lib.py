@@ -32,6 +32,8 @@ SIGNATURES = {
     "sb_spmm_csr_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "sb_spmm_csr_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _int,
                                _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _sz, _ptr]),
+    "sb_spmm_csr_acc_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _int,
+                                   _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _sz, _ptr]),
     "sb_spmm_csr_typed": (_int, [_int, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                  _i64, _ptr]),
     "sb_spmv_csr_scratch_bytes": (_sz, [_i64]),

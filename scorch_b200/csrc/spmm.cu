@@ -19,6 +19,11 @@
 #define SB_SPMM_INFLIGHT 32
 #endif
 
+// mean stored entries per row below which a launch takes several rows per warp
+#ifndef SB_SPMM_SHORT_ROW_MEAN
+#define SB_SPMM_SHORT_ROW_MEAN 24
+#endif
+
 namespace sb {
 
 constexpr int kWarpsPerCta = 8;
@@ -244,6 +249,20 @@ spmm_rows_kernel(SpmmArgs a) {
 #pragma unroll
       for (int w = 0; w < W; w++) acc[v].v[w] = 0.f;
     }
+    float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
+    if (a.accumulate && lane < L) {
+      // the row's present contents start the first lane group's sums: the load overlaps the
+      // index loads and gathers instead of sitting between the reduction and the store
+#pragma unroll
+      for (int v = 0; v < VEC; v++) {
+        if (!col_ok[v]) continue;
+#pragma unroll
+        for (int w = 0; w < W; w += 4) {
+          const float4 old = *reinterpret_cast<const float4*>(crow + col0 + v * L * W + w);
+          acc[v].v[w] = old.x; acc[v].v[w + 1] = old.y; acc[v].v[w + 2] = old.z; acc[v].v[w + 3] = old.w;
+        }
+      }
+    }
     int fj = 0;
     float fa = 0.f;
     if (R > 1) {
@@ -256,18 +275,10 @@ spmm_rows_kernel(SpmmArgs a) {
                                              b, e, lane, col_ok, a.ent, a.val_compact != 0, R > 1, fj, fa);
     reduce_groups<L, VEC, W>(acc);
     if (lane < L) {
-      float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
 #pragma unroll
       for (int v = 0; v < VEC; v++) {
         const int col = col0 + v * L * W;
         if (!col_ok[v]) continue;
-        if (a.accumulate) {
-#pragma unroll
-          for (int w = 0; w < W; w += 4) {
-            const float4 old = *reinterpret_cast<const float4*>(crow + col + w);
-            acc[v].v[w] += old.x; acc[v].v[w + 1] += old.y; acc[v].v[w + 2] += old.z; acc[v].v[w + 3] += old.w;
-          }
-        }
         st_stream<W>(crow + col, epilogue<W>(acc[v], a.bias, col, a.relu));
       }
     }
@@ -336,8 +347,15 @@ spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
       const int col = col0 + v * L * W;
       if (!col_ok[v]) continue;
       if (nseg == 1) {
-        st_stream<W>(a.C + bz * a.stride_c + (long long)row * a.ldc + col,
-                     epilogue<W>(s, a.bias, col, a.relu));
+        float* dst = a.C + bz * a.stride_c + (long long)row * a.ldc + col;
+        if (a.accumulate) {
+#pragma unroll
+          for (int w = 0; w < W; w += 4) {
+            const float4 old = *reinterpret_cast<const float4*>(dst + w);
+            s.v[w] += old.x; s.v[w + 1] += old.y; s.v[w + 2] += old.z; s.v[w + 3] += old.w;
+          }
+        }
+        st_stream<W>(dst, epilogue<W>(s, a.bias, col, a.relu));
       } else {
         float* dst = h.scratch + bz * h.scratch_batch + (long long)seg * a.k + col;
 #pragma unroll
@@ -363,6 +381,10 @@ __global__ void spmm_heavy_finalize_kernel(SpmmArgs a, HeavyArgs h) {
   for (int col = threadIdx.x * 4; col < a.k; col += blockDim.x * 4) {
     Pack<4> s;
     s.v[0] = s.v[1] = s.v[2] = s.v[3] = 0.f;
+    if (a.accumulate) {
+      const float4 old = *reinterpret_cast<const float4*>(crow + col);
+      s.v[0] = old.x; s.v[1] = old.y; s.v[2] = old.z; s.v[3] = old.w;
+    }
     for (int t = 0; t < nseg; t++) {
       const float4 v = *reinterpret_cast<const float4*>(src + (long long)t * a.k + col);
       s.v[0] += v.x; s.v[1] += v.y; s.v[2] += v.z; s.v[3] += v.w;
@@ -516,11 +538,12 @@ size_t sb_spmm_csr_scratch_bytes(int64_t segments, int64_t k, int64_t batch) {
   return (size_t)segments * (size_t)k * (size_t)batch * sizeof(float);
 }
 
-int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
-                    const int32_t* crd, const float* val, const float* B, int64_t ldb,
-                    const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
-                    int64_t stride_val, int64_t stride_b, int64_t stride_c, const void* plan,
-                    int64_t plan_segments, void* scratch, size_t scratch_bytes, void* stream) {
+static int spmm_csr_f32_impl(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                             const int32_t* crd, const float* val, const float* B, int64_t ldb,
+                             const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
+                             int64_t stride_val, int64_t stride_b, int64_t stride_c,
+                             const void* plan, int64_t plan_segments, void* scratch,
+                             size_t scratch_bytes, int accumulate, void* stream) {
   int rc = check_common(m, n, k, nnz, pos, crd, val, B, ldb, C, ldc);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(batch >= 1 && batch <= 65535, "spmm: batch must be in [1, 65535]");
@@ -532,6 +555,10 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
                       aligned16(C) && (!bias || aligned16(bias)) && (stride_b % 4 == 0) &&
                       (stride_c % 4 == 0) && ldb < (1ll << 32);
   if (!vec_ok) {
+    if (accumulate)
+      return fail(SB_ERR_UNSUPPORTED,
+                  "spmm: accumulation needs the vector layout (k, ldb, ldc multiples of 4; B, C "
+                  "16-byte aligned)");
     return launch_generic<float>(m, k, pos, crd, val, B, ldb, bias, relu, C, ldc, batch,
                                  stride_val, stride_b, stride_c, st);
   }
@@ -552,9 +579,30 @@ int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t*
   a.skip_heavy = (plan && plan_segments != 0) ? 1 : 0;
   a.ent = nullptr;
   a.val_compact = 0;
-  a.accumulate = 0;
-  a.short_rows = 0;
+  a.accumulate = accumulate ? 1 : 0;
+  // many short rows (e.g. one row chunk's share of a matrix): several rows per warp
+  a.short_rows = (nnz < (int64_t)SB_SPMM_SHORT_ROW_MEAN * m) ? 1 : 0;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, plan, nnz, plan_segments, scratch, st);
+}
+
+int sb_spmm_csr_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                    const int32_t* crd, const float* val, const float* B, int64_t ldb,
+                    const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
+                    int64_t stride_val, int64_t stride_b, int64_t stride_c, const void* plan,
+                    int64_t plan_segments, void* scratch, size_t scratch_bytes, void* stream) {
+  return spmm_csr_f32_impl(m, n, k, nnz, pos, crd, val, B, ldb, bias, relu, C, ldc, batch,
+                           stride_val, stride_b, stride_c, plan, plan_segments, scratch,
+                           scratch_bytes, 0, stream);
+}
+
+int sb_spmm_csr_acc_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,
+                        const int32_t* crd, const float* val, const float* B, int64_t ldb,
+                        const float* bias, int relu, float* C, int64_t ldc, int64_t batch,
+                        int64_t stride_val, int64_t stride_b, int64_t stride_c, const void* plan,
+                        int64_t plan_segments, void* scratch, size_t scratch_bytes, void* stream) {
+  return spmm_csr_f32_impl(m, n, k, nnz, pos, crd, val, B, ldb, bias, relu, C, ldc, batch,
+                           stride_val, stride_b, stride_c, plan, plan_segments, scratch,
+                           scratch_bytes, 1, stream);
 }
 
 int sb_spmm_csr_typed(int dtype, int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,

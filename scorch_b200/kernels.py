@@ -218,10 +218,11 @@ def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
 
 def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[CsrPlan] = None,
              out: Optional[torch.Tensor] = None, n: Optional[int] = None,
-             block_plan: Optional[BlockPlan] = None) -> torch.Tensor:
+             block_plan: Optional[BlockPlan] = None, accumulate: bool = False) -> torch.Tensor:
     """C = act(bias + A @ B) for CSR A.  ``B`` is (n, k) or (batch, n, k); ``val`` is (nnz,) —
     shared by all batch items — or (batch, nnz).  Returns (m, k) or (batch, m, k).
-    2-D ``B`` / ``out`` may be column slices of wider row-major buffers (row pitch > k)."""
+    2-D ``B`` / ``out`` may be column slices of wider row-major buffers (row pitch > k).
+    ``accumulate``: act(bias + out + A @ B), ``out`` required."""
     pos = _dev(pos, torch.int32, "pos")
     crd = _dev(crd, torch.int32, "crd")
     m, nnz = pos.numel() - 1, crd.numel()
@@ -262,10 +263,12 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
             if out.stride(1) != 1 or out.stride(0) < k:
                 raise ValueError("out rows must be contiguous")
             ldc = out.stride(0)
+    if accumulate and out is None:
+        raise ValueError("accumulate needs the tensor to add to (out=)")
     if plan is None:
         plan = plan_for(pos, nnz)
     L = _lib.lib()
-    if (block_plan is not None and block_plan.blocks > 0 and plan.segments == 0
+    if (block_plan is not None and not accumulate and block_plan.blocks > 0 and plan.segments == 0
             and k in _BLOCKED_SPMM_K and ldb % 4 == 0 and ldc % 4 == 0):
         with torch.cuda.device(B.device):
             check(L.sb_spmm_csr_blocked_f32(m, nb if n is None else n, k, nnz, pos.data_ptr(),
@@ -277,11 +280,11 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
     sbytes = L.sb_spmm_csr_scratch_bytes(plan.segments, k, batch)
     scratch = plan.scratch(sbytes) if sbytes else None
     with torch.cuda.device(B.device):
-        check(L.sb_spmm_csr_f32(m, nb if n is None else n, k, nnz, pos.data_ptr(), crd.data_ptr(),
-                                val.data_ptr(), B.data_ptr(), ldb, _ptr(bias), int(bool(relu)),
-                                out.data_ptr(), ldc, batch, stride_val, nb * k, m * k,
-                                plan.buf.data_ptr(), plan.segments, _ptr(scratch), sbytes,
-                                _stream()))
+        fn = L.sb_spmm_csr_acc_f32 if accumulate else L.sb_spmm_csr_f32
+        check(fn(m, nb if n is None else n, k, nnz, pos.data_ptr(), crd.data_ptr(),
+                 val.data_ptr(), B.data_ptr(), ldb, _ptr(bias), int(bool(relu)),
+                 out.data_ptr(), ldc, batch, stride_val, nb * k, m * k,
+                 plan.buf.data_ptr(), plan.segments, _ptr(scratch), sbytes, _stream()))
     return out
 
 

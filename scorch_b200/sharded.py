@@ -5,20 +5,33 @@ csrc/spmm.h:2035-2077); this module is the multi-GPU form of the same products:
 
 * rows of the sparse matrix are cut into contiguous blocks balanced by stored entries
   (``sb_partition_rows_by_nnz``); rank g owns block g and computes those output rows;
+* a product whose dense operand is the same on every rank (weights, a replicated feature matrix)
+  needs no communication: ``row_block`` + the SpMM kernel on the local rows
+  (``sharded_spmm_replicated``);
 * the dense operand of a GCN layer is produced row-sharded by the previous layer, so every
-  layer all-gathers it (NCCL over NVLink).  The gather is cut into column panels and issued on
-  a side stream: the SpMM over panel p runs while panel p+1 is still in flight, and the local
-  dense transform X·W (cuBLAS through torch) of later panels overlaps both;
-* blocks have different row counts, so each rank's block is padded to the largest block in the
-  gathered buffer and the matrix's column indices are remapped ONCE, at set-up, to that padded
-  layout (column j of rank r's block -> r*max_rows + (j - start_r)).  Nothing is repacked at
-  run time and the gathered panel lands in local HBM before any kernel reads it.
+  layer all-gathers it (NCCL over NVLink).  The gather is cut into ROW CHUNKS: every rank's
+  block of operand rows is cut into ``chunks`` equal pieces, gather c collects piece c of every
+  rank, and the rank's matrix block is split once, at set-up, into ``chunks`` sub-matrices, the
+  c-th holding the entries whose column falls into piece c of its owner.  The layer is then
 
-``spmm_fn`` lets the CPU tests (gloo, world size 2) run this host logic with the oracle's SpMM;
-the default is the CUDA kernel.
+      C  = A_0 G_0;   C += A_1 G_1;   ...;   C = act(C + A_last G_last)
+
+  with gather c+1 in flight on a communication stream while sub-matrix c is multiplied.  Every
+  pass reads full-width operand rows (1 KB at 256 columns) and reads its part of the matrix
+  once; the random gathers of one pass are confined to one chunk of the operand, which the L2
+  cache holds a good part of;
+* blocks have different row counts, so each rank's block is padded to ``chunks * chunk_rows``
+  rows and the column indices are remapped ONCE, at set-up, to the gathered layout of their
+  chunk (column j, owned by rank q at offset o, chunk c = o // chunk_rows, becomes
+  q * chunk_rows + o - c * chunk_rows).  Nothing is repacked at run time and gathered data
+  always lands in local HBM before a kernel reads it.
+
+``spmm_fn`` lets the CPU tests (gloo) run this host logic with a CPU SpMM; the default is the
+CUDA kernel.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional
 
@@ -40,18 +53,60 @@ def row_bounds(pos: torch.Tensor, parts: int) -> List[int]:
 
 
 @dataclass
+class CsrBlock:
+    """A CSR matrix with the state the SpMM wrapper caches for it."""
+    pos: torch.Tensor          # int32 [rows + 1]
+    crd: torch.Tensor          # int32 [nnz]
+    val: torch.Tensor
+    plan: object = None
+
+    @property
+    def rows(self) -> int:
+        return self.pos.numel() - 1
+
+    @property
+    def nnz(self) -> int:
+        return int(self.crd.numel())
+
+
+def row_block(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, rank: int, world: int,
+              bounds: Optional[List[int]] = None):
+    """Rank's nnz-balanced row block of a CSR matrix, columns untouched: (CsrBlock, bounds)."""
+    bounds = row_bounds(pos, world) if bounds is None else bounds
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    p0, p1 = int(pos[r0]), int(pos[r1])
+    lpos = (pos[r0:r1 + 1] - p0).to(torch.int32).contiguous()
+    return CsrBlock(lpos, crd[p0:p1].contiguous(), val[p0:p1].contiguous()), bounds
+
+
+def default_chunks(world: int) -> int:
+    """Row chunks per layer: none with one rank (nothing to overlap), eight otherwise."""
+    env = os.environ.get("SCORCH_B200_GCN_CHUNKS")
+    if env:
+        return max(1, int(env))
+    return 1 if world == 1 else 8
+
+
+@dataclass
 class ShardedCsr:
-    """One rank's row block of a CSR matrix, columns remapped to the padded gathered layout."""
+    """One rank's row block of a square CSR matrix, split by operand row chunk."""
     rank: int
     world: int
     bounds: List[int]          # world+1 row bounds of the global matrix
-    max_rows: int              # rows per rank in the padded gathered layout
-    pos: torch.Tensor          # int32 [rows_local + 1], rebased to 0
-    crd: torch.Tensor          # int32 [nnz_local], remapped
-    val: torch.Tensor
+    chunk_rows: int            # operand rows per rank in one chunk
+    blocks: List[CsrBlock]     # one sub-matrix per chunk, columns in the chunk's gathered layout
     n_global: int
-    plan: object = None
+    local: CsrBlock            # the unsplit row block with global column indices
     _buffers: dict = field(default_factory=dict)
+
+    @property
+    def chunks(self) -> int:
+        return len(self.blocks)
+
+    @property
+    def max_rows(self) -> int:
+        """Rows per rank in the padded layout (chunks * chunk_rows >= the largest block)."""
+        return self.chunks * self.chunk_rows
 
     @property
     def rows(self) -> int:
@@ -59,27 +114,22 @@ class ShardedCsr:
 
     @property
     def nnz(self) -> int:
-        return int(self.crd.numel())
+        return self.local.nnz
 
     @staticmethod
     def from_global(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, rank: int, world: int,
-                    n_cols: Optional[int] = None) -> "ShardedCsr":
+                    n_cols: Optional[int] = None, chunks: Optional[int] = None) -> "ShardedCsr":
         m = pos.numel() - 1
         n_cols = m if n_cols is None else n_cols
         if n_cols != m:
-            raise ValueError("sharded layers need a square matrix (features are sharded like rows)")
-        bounds = row_bounds(pos, world)
-        r0, r1 = bounds[rank], bounds[rank + 1]
-        p0, p1 = int(pos[r0]), int(pos[r1])
-        lpos = (pos[r0:r1 + 1] - p0).to(torch.int32).contiguous()
-        lcrd = crd[p0:p1]
-        max_rows = max(bounds[g + 1] - bounds[g] for g in range(world))
-        if world > 1:
-            starts = torch.tensor(bounds[:-1], dtype=torch.int64, device=crd.device)
-            owner = torch.bucketize(lcrd.to(torch.int64), starts, right=True) - 1
-            lcrd = (owner * max_rows + (lcrd.to(torch.int64) - starts[owner])).to(torch.int32)
-        return ShardedCsr(rank, world, bounds, max_rows, lpos, lcrd.contiguous(),
-                          val[p0:p1].contiguous(), m)
+            raise ValueError("sharded layers need a square matrix (features are sharded like rows); "
+                             "use row_block / sharded_spmm_replicated for a replicated operand")
+        local, bounds = row_block(pos, crd, val, rank, world)
+        chunks = default_chunks(world) if chunks is None else max(1, int(chunks))
+        largest = max(bounds[g + 1] - bounds[g] for g in range(world))
+        chunk_rows = max(1, -(-largest // chunks))
+        blocks = _split_by_chunk(local, bounds, chunk_rows, chunks)
+        return ShardedCsr(rank, world, bounds, chunk_rows, blocks, m, local)
 
     def buffer(self, name: str, shape, device) -> torch.Tensor:
         key = (name, tuple(shape))
@@ -90,40 +140,117 @@ class ShardedCsr:
         return buf
 
 
-def _default_spmm(shard: ShardedCsr, B: torch.Tensor, out: torch.Tensor, relu: bool) -> None:
-    from . import kernels as K
-    if shard.plan is None:
-        shard.plan = K.CsrPlan(shard.pos, shard.nnz)
-    K.spmm_csr(shard.pos, shard.crd, shard.val, B, relu=relu, plan=shard.plan, out=out)
-
-
-def _panels(k: int, widths) -> List[tuple]:
-    """(first column, width) of each column panel; ``widths`` is an int or a sequence that is
-    repeated/truncated to cover k columns."""
-    if isinstance(widths, int):
-        widths = [widths]
-    out, c, i = [], 0, 0
-    while c < k:
-        w = min(int(widths[min(i, len(widths) - 1)]), k - c)
-        out.append((c, w))
-        c += w
-        i += 1
+def _split_by_chunk(local: CsrBlock, bounds: List[int], chunk_rows: int, chunks: int) -> List[CsrBlock]:
+    """Sub-matrix c keeps the entries whose column lies in rows [c*chunk_rows, (c+1)*chunk_rows)
+    of its owner's block, renumbered to the layout an all-gather of those pieces produces.
+    Columns stay ascending within a row (owner, then offset, is the global order)."""
+    dev = local.crd.device
+    rows = local.rows
+    starts = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
+    j = local.crd.to(torch.int64)
+    owner = torch.bucketize(j, starts, right=True) - 1
+    off = j - starts[owner]
+    del j
+    c = torch.div(off, chunk_rows, rounding_mode="floor")
+    newcol = (owner * chunk_rows + (off - c * chunk_rows)).to(torch.int32)
+    del owner, off
+    if chunks == 1:
+        return [CsrBlock(local.pos, newcol, local.val)]
+    lens = (local.pos[1:] - local.pos[:-1]).to(torch.int64)
+    row = torch.repeat_interleave(torch.arange(rows, dtype=torch.int64, device=dev), lens)
+    key = c * rows + row
+    del c, row
+    order = torch.sort(key, stable=True).indices
+    counts = torch.bincount(key, minlength=chunks * rows)
+    del key
+    crd_s, val_s = newcol[order].contiguous(), local.val[order].contiguous()
+    del order, newcol
+    pos_all = torch.zeros(chunks * rows + 1, dtype=torch.int64, device=dev)
+    pos_all[1:] = torch.cumsum(counts, 0)
+    cuts = pos_all[::rows][:chunks + 1].tolist() if rows else [0] * (chunks + 1)
+    out = []
+    for ci in range(chunks):
+        e0, e1 = int(cuts[ci]), int(cuts[ci + 1])
+        p = (pos_all[ci * rows: ci * rows + rows + 1] - e0).to(torch.int32).contiguous()
+        out.append(CsrBlock(p, crd_s[e0:e1], val_s[e0:e1]))
     return out
 
 
+def _default_spmm(block: CsrBlock, B: torch.Tensor, out: torch.Tensor, relu: bool,
+                  accumulate: bool = False) -> None:
+    from . import kernels as K
+    if block.plan is None:
+        block.plan = K.CsrPlan(block.pos, block.nnz)
+    K.spmm_csr(block.pos, block.crd, block.val, B, relu=relu, plan=block.plan, out=out,
+               accumulate=accumulate)
+
+
+def sharded_spmm_replicated(block: CsrBlock, B: torch.Tensor, bias=None, relu: bool = False,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """This rank's rows of act(bias + A B) for a dense operand every rank holds (a weight matrix,
+    a replicated feature matrix): no communication, any matrix shape."""
+    from . import kernels as K
+    if block.plan is None:
+        block.plan = K.CsrPlan(block.pos, block.nnz)
+    return K.spmm_csr(block.pos, block.crd, block.val, B, bias=bias, relu=relu, plan=block.plan, out=out)
+
+
+class Timeline:
+    """Optional per-step record of where a sharded forward spends its time: CUDA events around
+    the dense transforms, the waits for gathered chunks and the SpMM launches on the main stream,
+    and around each all-gather on the communication stream.  ``summary()`` synchronises."""
+
+    def __init__(self):
+        self.spans = []   # (label, start event, end event)
+        self.steps = 0
+
+    def span(self, label: str, stream=None):
+        return _Span(self, label, stream)
+
+    def summary(self) -> dict:
+        """Mean milliseconds per step and label."""
+        out = {}
+        for label, a, b in self.spans:
+            b.synchronize()
+            out[label] = out.get(label, 0.0) + a.elapsed_time(b)
+        steps = max(1, self.steps)
+        return {k: v / steps for k, v in out.items()}
+
+
+class _Span:
+    def __init__(self, tl: Optional[Timeline], label: str, stream):
+        self.tl, self.label, self.stream = tl, label, stream
+
+    def __enter__(self):
+        if self.tl is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.a.record(self.stream)
+        return self
+
+    def __exit__(self, *exc):
+        if self.tl is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record(self.stream)
+            self.tl.spans.append((self.label, self.a, b))
+        return False
+
+
+def _span(tl: Optional[Timeline], label: str, stream=None):
+    return _Span(tl, label, stream)
+
+
 class _Gatherer:
-    """Issues one panel's all-gather on the communication stream and hands back the event the
+    """Issues one chunk's all-gather on the communication stream and hands back the event the
     consumer has to wait for."""
 
-    def __init__(self, shard: ShardedCsr, dev, group):
-        self.shard, self.dev, self.group = shard, dev, group
+    def __init__(self, shard: ShardedCsr, dev, group, timeline: Optional[Timeline] = None):
+        self.shard, self.dev, self.group, self.tl = shard, dev, group, timeline
         self.on_gpu = dev.type == "cuda"
         self.comm = None
         if self.on_gpu and shard.world > 1:
             self.comm = shard._buffers.get("comm_stream")
             if self.comm is None:
                 # high priority: the gather's few CTAs are placed ahead of the SpMM's pending ones
-                # (measured 2.5 % on the 8-GPU forward)
                 self.comm = shard._buffers["comm_stream"] = torch.cuda.Stream(device=dev, priority=-1)
         self.main = torch.cuda.current_stream(dev) if self.on_gpu else None
 
@@ -132,7 +259,7 @@ class _Gatherer:
         shard = self.shard
         if shard.world == 1:
             return send, None
-        buf = shard.buffer(name, (shard.world * shard.max_rows, send.shape[1]), self.dev)
+        buf = shard.buffer(name, (shard.world * send.shape[0], send.shape[1]), self.dev)
         if self.comm is None:
             dist.all_gather_into_tensor(buf, send, group=self.group)
             return buf, None
@@ -140,110 +267,97 @@ class _Gatherer:
         produced.record(self.main)
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(produced)
-            dist.all_gather_into_tensor(buf, send, group=self.group)
+            with _span(self.tl if self.on_gpu else None, "all_gather", self.comm):
+                dist.all_gather_into_tensor(buf, send, group=self.group)
             done = torch.cuda.Event()
             done.record(self.comm)
         return buf, done
 
     def wait(self, event) -> None:
         if event is not None:
-            self.main.wait_event(event)
+            with _span(self.tl, "wait_for_gather", self.main):
+                self.main.wait_event(event)
+
+
+def _chunk_rows(shard: ShardedCsr, c: int):
+    """Local row range whose transform fills piece c of the send buffer."""
+    lo = min(c * shard.chunk_rows, shard.rows)
+    hi = min((c + 1) * shard.chunk_rows, shard.rows)
+    return lo, hi
+
+
+def _pipelined_layer(shard: ShardedCsr, g: _Gatherer, name: str, x_local: torch.Tensor,
+                     weight: Optional[torch.Tensor], out: torch.Tensor, relu: bool,
+                     spmm_fn: Callable, lookahead: int, tl: Optional[Timeline], label: str) -> None:
+    """out = act(A (x_local W)) over this rank's rows, chunk by chunk (W = None: act(A x))."""
+    S, Rc, dev = shard.chunks, shard.chunk_rows, x_local.device
+    k = out.shape[1]
+    send = shard.buffer(name + "send", (S * Rc, k), dev)
+    pending = []
+    tlg = tl if dev.type == "cuda" else None
+
+    def produce(c):
+        lo, hi = _chunk_rows(shard, c)
+        if hi > lo:
+            with _span(tlg, "dense_transform"):
+                if weight is not None:
+                    torch.matmul(x_local[lo:hi], weight, out=send[lo:hi])
+                else:
+                    send[lo:hi].copy_(x_local[lo:hi])
+        pending.append(g.gather(f"{name}recv{c}", send[c * Rc:(c + 1) * Rc]))
+
+    def consume(c):
+        buf, ev = pending[c]
+        g.wait(ev)
+        with _span(tlg, label):
+            spmm_fn(shard.blocks[c], buf, out, relu and c == S - 1, c > 0)
+
+    for c in range(S):
+        produce(c)
+        if c >= lookahead:
+            consume(c - lookahead)
+    for c in range(max(0, S - lookahead), S):
+        consume(c)
 
 
 def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[torch.Tensor],
-                  relu: bool = False, panel=64, group=None,
-                  spmm_fn: Optional[Callable] = None) -> torch.Tensor:
+                  relu: bool = False, group=None, spmm_fn: Optional[Callable] = None,
+                  lookahead: int = 2, timeline: Optional[Timeline] = None) -> torch.Tensor:
     """Rows [bounds[rank], bounds[rank+1]) of  act(A (X W))  (W = None: act(A X)).
 
-    ``x_local`` holds this rank's rows of X.  Per column panel: local transform into the send
-    buffer, all-gather into the padded (world*max_rows, panel) receive buffer on the
-    communication stream, SpMM of the local row block over that panel as soon as it has arrived.
-    """
+    ``x_local`` holds this rank's rows of X.  Per row chunk: local transform into the send
+    buffer, all-gather of that piece from every rank on the communication stream, SpMM of the
+    chunk's sub-matrix (accumulating into the output) as soon as the piece has arrived."""
     spmm_fn = spmm_fn or _default_spmm
-    rows, dev = shard.rows, x_local.device
+    dev = x_local.device
     k = weight.shape[1] if weight is not None else x_local.shape[1]
-    panels = _panels(k, k if shard.world == 1 else panel)
-    out = torch.empty((rows, k), dtype=torch.float32, device=dev)
-    g = _Gatherer(shard, dev, group)
-    pending = []
-    for idx, (c, w) in enumerate(panels):
-        send = shard.buffer(f"send{idx}", (shard.max_rows, w), dev)
-        if weight is not None:
-            torch.matmul(x_local, weight[:, c:c + w], out=send[:rows])
-        else:
-            send[:rows].copy_(x_local[:, c:c + w])
-        pending.append(g.gather(f"recv{idx}", send))
-    for idx, (c, w) in enumerate(panels):
-        buf, ev = pending[idx]
-        g.wait(ev)
-        spmm_fn(shard, buf, out[:, c:c + w], relu)
+    out = torch.empty((shard.rows, k), dtype=torch.float32, device=dev)
+    g = _Gatherer(shard, dev, group, timeline)
+    _pipelined_layer(shard, g, f"layer{k}", x_local, weight, out, relu, spmm_fn, lookahead, timeline, "spmm")
     return out
 
 
 def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor,
-                        panel=(32, 32, 64), panel2=32, group=None,
-                        spmm_fn: Optional[Callable] = None) -> torch.Tensor:
-    """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329).
+                        group=None, spmm_fn: Optional[Callable] = None, lookahead: int = 2,
+                        timeline: Optional[Timeline] = None) -> torch.Tensor:
+    """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329;
+    transform first, then the sparse product, as there).
 
-    Both layers run as one pipeline so that as little communication as possible is exposed:
-      * layer 1 is cut into column panels (a narrow first one shortens the pipeline fill); panel
-        p's transform X W1[:, p] is all-gathered while the SpMM of panel p-1 runs;
-      * as soon as a panel of H = ReLU(A_hat ...) is final, its contribution H_p W2[p, :] is
-        accumulated into layer 2's send buffers, so after the last SpMM only a thin GEMM is left
-        before layer 2's gathers can start;
-      * layer 2 is cut into two panels so that the second gather overlaps the first SpMM.
-    With one rank there is nothing to gather and every layer is a single full-width SpMM.
-    """
+    Per layer the local transform of row chunk c (cuBLAS through torch) is all-gathered while the
+    sub-matrices of earlier chunks are multiplied; transforms run ``lookahead`` chunks ahead of
+    the SpMMs on the main stream so that the communication stream always has a gather queued.
+    Exposed communication is one chunk's transform + gather at the start of each layer.  With one
+    rank and one chunk every layer is a single full-width SpMM."""
     spmm_fn = spmm_fn or _default_spmm
-    rows, dev, world = shard.rows, x_local.device, shard.world
+    dev = x_local.device
     k1, k2 = W1.shape[1], W2.shape[1]
-    if world == 1:
-        panel, panel2 = k1, k2
-    elif world == 2 and panel == (32, 32, 64) and panel2 == 32:
-        panel, panel2 = 64, k2   # two ranks: the gather hides behind SpMM anyway; wider panels are cheaper
-    p1, p2 = _panels(k1, panel), _panels(k2, panel2)
-    g = _Gatherer(shard, dev, group)
-    H = shard.buffer("hidden", (rows, k1), dev)
-    out = torch.empty((rows, k2), dtype=torch.float32, device=dev)
-
-    send2 = [shard.buffer(f"l2send{j}", (shard.max_rows, w), dev) for j, (_, w) in enumerate(p2)]
-    pending, pending2 = [], []
-
-    def produce(i):   # layer-1 transform of panel i and its gather
-        c, w = p1[i]
-        send = shard.buffer(f"l1send{i}", (shard.max_rows, w), dev)
-        torch.matmul(x_local, W1[:, c:c + w], out=send[:rows])
-        pending.append(g.gather(f"l1recv{i}", send))
-
-    def consume(i):   # SpMM of panel i, then its contribution to layer 2's operands
-        c, w = p1[i]
-        buf, ev = pending[i]
-        g.wait(ev)
-        hp = H[:, c:c + w]
-        spmm_fn(shard, buf, hp, True)
-        last = i == len(p1) - 1
-        for j, (c2, w2) in enumerate(p2):
-            dst = send2[j][:rows]
-            if i == 0:
-                torch.matmul(hp, W2[c:c + w, c2:c2 + w2], out=dst)
-            else:
-                dst.addmm_(hp, W2[c:c + w, c2:c2 + w2])
-            if last:
-                pending2.append(g.gather(f"l2recv{j}", send2[j]))
-
-    # transforms run `lookahead` panels ahead of the SpMMs on the main stream: the first SpMM is
-    # issued when its gather is about to land instead of behind every transform
-    lookahead = 2
-    for i in range(len(p1)):
-        produce(i)
-        if i >= lookahead:
-            consume(i - lookahead)
-    for i in range(max(0, len(p1) - lookahead), len(p1)):
-        consume(i)
-    for j, (c2, w2) in enumerate(p2):
-        buf, ev = pending2[j]
-        g.wait(ev)
-        spmm_fn(shard, buf, out[:, c2:c2 + w2], False)
+    g = _Gatherer(shard, dev, group, timeline)
+    H = shard.buffer("hidden", (shard.rows, k1), dev)
+    out = torch.empty((shard.rows, k2), dtype=torch.float32, device=dev)
+    _pipelined_layer(shard, g, "l1", x_local, W1, H, True, spmm_fn, lookahead, timeline, "spmm_layer1")
+    _pipelined_layer(shard, g, "l2", H, W2, out, False, spmm_fn, lookahead, timeline, "spmm_layer2")
+    if timeline is not None:
+        timeline.steps += 1
     return out
 
 
@@ -252,10 +366,11 @@ def gather_rows(shard: ShardedCsr, local: torch.Tensor, group=None) -> torch.Ten
     if shard.world == 1:
         return local
     k = local.shape[1]
-    send = torch.zeros((shard.max_rows, k), dtype=local.dtype, device=local.device)
+    largest = max(shard.bounds[g + 1] - shard.bounds[g] for g in range(shard.world))
+    send = torch.zeros((largest, k), dtype=local.dtype, device=local.device)
     send[:shard.rows] = local
-    buf = torch.empty((shard.world * shard.max_rows, k), dtype=local.dtype, device=local.device)
+    buf = torch.empty((shard.world * largest, k), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, send, group=group)
-    parts = [buf[g * shard.max_rows: g * shard.max_rows + (shard.bounds[g + 1] - shard.bounds[g])]
+    parts = [buf[g * largest: g * largest + (shard.bounds[g + 1] - shard.bounds[g])]
              for g in range(shard.world)]
     return torch.cat(parts, 0)

@@ -124,6 +124,33 @@ def test_spmm_heavy_rows_and_plan(oracle, k):
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("k", [64, 256])
+def test_spmm_accumulating_form(oracle, k):
+    """sb_spmm_csr_acc_f32: act(bias + C + A B) with short, empty and multi-segment heavy rows."""
+    from scorch_b200 import kernels as K
+    from scorch_b200._lib import HEAVY_ROW_NNZ as T
+    m, n = 50, 5000
+    lens = np.full(m, 11)
+    lens[[2, 9, 30]] = [T + 5, 3 * T + 1, 0]
+    pos, crd, val = random_csr(m, n, lens, seed=21)
+    val = (val / np.sqrt(np.repeat(np.maximum(lens, 1), lens))).astype(np.float32)
+    rng = np.random.default_rng(22)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    C0 = rng.standard_normal((m, k)).astype(np.float32)
+    bias = rng.standard_normal(k).astype(np.float32)
+    for relu in (False, True):
+        out = dev(C0.copy())
+        got = K.spmm_csr(dev(pos), dev(crd), dev(val), dev(B), bias=dev(bias), relu=relu, out=out,
+                         accumulate=True)
+        assert got.data_ptr() == out.data_ptr()
+        want = oracle.spmm_csr_acc64(pos, crd, val, B) + C0.astype(np.float64) + bias.astype(np.float64)
+        if relu:
+            want = np.maximum(want, 0)
+        assert_close(oracle, got, want, f"accumulate relu={relu}")
+    with pytest.raises(ValueError):
+        K.spmm_csr(dev(pos), dev(crd), dev(val), dev(B), accumulate=True)
+
+
 def test_spmm_batched_shared_structure(oracle):
     from scorch_b200 import kernels as K
     rng = np.random.default_rng(5)

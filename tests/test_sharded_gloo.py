@@ -1,5 +1,6 @@
-"""Host logic of the row-sharded layers (partition, padded all-gather layout, column remap,
-panel loop) on CPU ranks: world size 2 and 3 over gloo, the oracle standing in for the CUDA SpMM."""
+"""Host logic of the row-sharded layers (partition, padded all-gather layout, split of the row
+block by operand row chunk, column remap, chunk loop with accumulation) on CPU ranks: world size
+2 and 3 over gloo, the oracle standing in for the CUDA SpMM."""
 from __future__ import annotations
 
 import os
@@ -20,14 +21,18 @@ def _free_port() -> int:
     return port
 
 
-def _oracle_spmm(shard, B, out, relu):
+def _oracle_spmm(block, B, out, relu, accumulate=False):
     from oracle import oracle as O
-    r = O.spmm_csr_acc64(shard.pos.numpy(), shard.crd.numpy(), shard.val.numpy(),
-                         B.contiguous().numpy(), None, relu)
+    r = O.spmm_csr_acc64(block.pos.numpy(), block.crd.numpy(), block.val.numpy(),
+                         B.contiguous().numpy())
+    if accumulate:
+        r = r + out.numpy().astype(np.float64)
+    if relu:
+        r = np.maximum(r, 0)
     out.copy_(torch.from_numpy(r.astype(np.float32)))
 
 
-def _worker(rank, world, port, n, tmp):
+def _worker(rank, world, port, n, chunks, tmp):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -36,26 +41,27 @@ def _worker(rank, world, port, n, tmp):
         g = W.gcn_graph(n, mean_deg=6.0, max_deg=400, seed=0)
         X = W.randn_on((n, 24), seed=1)
         W1, W2 = W.glorot(24, 40, seed=0), W.glorot(40, 8, seed=1)
-        shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, world)
+        shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, world, chunks=chunks)
+        assert shard.chunks == chunks and sum(b.nnz for b in shard.blocks) == shard.nnz
         r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
-        out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, panel=(8, 16), panel2=4,
-                                    spmm_fn=_oracle_spmm)
-        one = S.sharded_layer(shard, X[r0:r1].contiguous(), W1, relu=True, panel=16, spmm_fn=_oracle_spmm)
+        out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, spmm_fn=_oracle_spmm)
+        one = S.sharded_layer(shard, X[r0:r1].contiguous(), W1, relu=True, spmm_fn=_oracle_spmm)
         assert one.shape == (r1 - r0, 40)
-        full = S.gather_rows(shard, out)
+        full, full_one = S.gather_rows(shard, out), S.gather_rows(shard, one)
         if rank == 0:
-            torch.save({"out": full, "bounds": shard.bounds, "max_rows": shard.max_rows}, tmp)
+            torch.save({"out": full, "one": full_one, "bounds": shard.bounds, "max_rows": shard.max_rows,
+                        "chunk_rows": shard.chunk_rows}, tmp)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_sharded_gcn_matches_single_process(tmp_path, world):
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (3, 4)])
+def test_sharded_gcn_matches_single_process(tmp_path, world, chunks):
     from oracle import oracle as O
     from scorch_b200 import sharded as S, workloads as W
     n = 1500
     tmp = str(tmp_path / "out.pt")
-    mp.spawn(_worker, args=(world, _free_port(), n, tmp), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), n, chunks, tmp), nprocs=world, join=True)
     got = torch.load(tmp)
     g = W.gcn_graph(n, mean_deg=6.0, max_deg=400, seed=0)
     X = W.randn_on((n, 24), seed=1)
@@ -64,12 +70,33 @@ def test_sharded_gcn_matches_single_process(tmp_path, world):
     h = O.spmm_csr_acc64(pos, crd, val, (X @ W1).numpy(), None, True).astype(np.float32)
     want = O.spmm_csr_acc64(pos, crd, val, (torch.from_numpy(h) @ W2).numpy())
     np.testing.assert_allclose(got["out"].numpy(), want, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(got["one"].numpy(), h, rtol=1e-4, atol=1e-5)
     # blocks are balanced by stored entries, contiguous and cover every row once
     b = got["bounds"]
     assert b[0] == 0 and b[-1] == n and all(b[i] <= b[i + 1] for i in range(world))
     nnz = np.diff(pos[np.array(b)])
     assert nnz.max() - nnz.min() <= 2 * np.diff(pos).max()
-    assert got["max_rows"] == max(b[i + 1] - b[i] for i in range(world))
+    largest = max(b[i + 1] - b[i] for i in range(world))
+    assert got["max_rows"] == chunks * got["chunk_rows"] >= largest > (chunks - 1) * got["chunk_rows"] - chunks
+
+
+def test_chunk_split_single_process_keeps_every_entry():
+    """One rank, several chunks: each sub-matrix holds the entries of its column range with
+    columns renumbered from the chunk's first row, ascending within a row."""
+    from scorch_b200 import sharded as S, workloads as W
+    n = 700
+    g = W.gcn_graph(n, mean_deg=5.0, max_deg=200, seed=3)
+    shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, 0, 1, chunks=4)
+    dense = torch.zeros((n, n), dtype=torch.float32)
+    for c, blk in enumerate(shard.blocks):
+        lens = (blk.pos[1:] - blk.pos[:-1]).long()
+        rows = torch.repeat_interleave(torch.arange(n), lens)
+        assert blk.nnz == 0 or int(blk.crd.max()) < shard.chunk_rows
+        d = (blk.crd[1:] - blk.crd[:-1])[rows[1:] == rows[:-1]]
+        assert bool((d > 0).all())
+        dense[rows, blk.crd.long() + c * shard.chunk_rows] += blk.val
+    want = g.torch_csr().to_dense()
+    assert torch.equal(dense, want)
 
 
 def test_row_bounds_host_matches_definition():
