@@ -622,10 +622,8 @@ class GcnSharded(Workload):
 
     @property
     def launches_per_step(self):
-        # per layer one SpMM call per row chunk; a call is the rows kernel, plus the heavy-segment
-        # kernel and its fix-up when the chunk's sub-matrix has heavy rows
-        per_layer = sum(3 if (b.plan is not None and b.plan.segments) else 1 for b in self.shard.blocks)
-        return 2 * per_layer
+        # per layer one SpMM launch per row chunk (rows and heavy-row segments share the launch)
+        return 2 * self.shard.chunks
 
     def begin_block(self):
         self.timeline = self.S.Timeline()

@@ -146,8 +146,9 @@ SB_API int sb_spmv_csr_typed(int dtype, int64_t m, int64_t n, int64_t nnz, const
  * lives in an array of SB_STATIC_SCRATCH_BYTES that is part of the library image, so each GPU
  * that loads the library holds that much memory until the process exits.
  *   - nnz above SB_STATIC_SPMV_MAX_NNZ is rejected with SB_ERR_UNSUPPORTED.
- *   - The first call on a device resolves the array's device address; make that call outside of
- *     any stream capture.
+ *   - The first call on a device resolves the array's device address and keeps it for the life
+ *     of the process; make that call outside of any stream capture, and do not use this entry
+ *     again after a cudaDeviceReset in the same process (the kept address is then stale).
  *   - All calls share the array: calls that overlap on one GPU (other streams, other threads)
  *     race.  Serialise them, or use sb_spmv_csr_f32 with buffers of your own. */
 #define SB_STATIC_SPMV_MAX_NNZ (1LL << 26)

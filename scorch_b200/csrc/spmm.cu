@@ -207,11 +207,10 @@ __device__ __forceinline__ Pack<W> epilogue(Pack<W> s, const float* bias, int co
 constexpr int kShortRowsPerWarp = 4;  // (2 and 8 measured slower)
 // (four CTAs per SM for the short-row form: 64 registers; five and three measured slower)
 template <int L, int VEC, int W, bool EXACT, int R>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, R > 1 ? 4 : 1)
-spmm_rows_kernel(SpmmArgs a) {
+__device__ __forceinline__ void rows_body(const SpmmArgs& a, int block_x) {
   constexpr int TILE = L * W * VEC;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row_base = (blockIdx.x * kWarpsPerCta + warp) * R;
+  const int row_base = (block_x * kWarpsPerCta + warp) * R;
   if (row_base >= a.m) return;
   const long long bz = blockIdx.z;
   const int l = lane % L;
@@ -285,23 +284,156 @@ spmm_rows_kernel(SpmmArgs a) {
   }
 }
 
+template <int L, int VEC, int W, bool EXACT, int R>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, R > 1 ? 4 : 1)
+spmm_rows_kernel(SpmmArgs a) {
+  rows_body<L, VEC, W, EXACT, R>(a, (int)blockIdx.x);
+}
+
+// Short rows, narrow tiles (L <= 16 lanes span the tile): each of the 32/L lane groups of a warp
+// takes a row of its own, so a warp works on 32/L rows at once and no sums cross lanes.  A group
+// reads its row's indices/values L at a time and keeps SB_SPMM_INFLIGHT floats of gathered
+// operand rows in flight per lane.  Rows longer than kGroupedMaxRow (but not heavy) are done by
+// the whole warp afterwards, like the general kernel does.
+#ifndef SB_SPMM_GROUPED_MAX_ROW
+#define SB_SPMM_GROUPED_MAX_ROW 64
+#endif
+constexpr int kGroupedMaxRow = SB_SPMM_GROUPED_MAX_ROW;
+
+template <int L, int W, bool EXACT>
+__device__ __forceinline__ void rows_grouped_body(const SpmmArgs& a, int block_x) {
+  constexpr int G = 32 / L;
+  constexpr int TILE = L * W;
+  constexpr int UMAX = SB_SPMM_INFLIGHT / W;
+  constexpr int U = (L < UMAX) ? L : UMAX;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_base = (block_x * kWarpsPerCta + warp) * G;
+  if (row_base >= a.m) return;
+  const int g = lane / L, l = lane % L;
+  const int row = row_base + g;
+  const long long bz = blockIdx.z;
+  const float* val = a.val + bz * a.stride_val;
+  const int col0 = blockIdx.y * TILE + l * W;
+  const bool col_ok = EXACT || col0 < a.k;
+  const float* Bcol = a.B + bz * a.stride_b + col0;
+  const unsigned ldb = (unsigned)a.ldb;
+  int b = 0, e = 0;
+  if (row < a.m) {
+    b = __ldg(a.pos + row);
+    e = __ldg(a.pos + row + 1);
+  }
+  const bool heavy = a.skip_heavy && (e - b) > SB_HEAVY_ROW_NNZ;
+  const bool by_warp = !heavy && (e - b) > kGroupedMaxRow;
+  const bool mine = row < a.m && !heavy && !by_warp;
+  const int ge = mine ? e : b;
+  float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
+  Pack<W> acc;
+#pragma unroll
+  for (int w = 0; w < W; w++) acc.v[w] = 0.f;
+  if (a.accumulate && mine && col_ok) {
+#pragma unroll
+    for (int w = 0; w < W; w += 4) {
+      const float4 old = *reinterpret_cast<const float4*>(crow + col0 + w);
+      acc.v[w] = old.x; acc.v[w + 1] = old.y; acc.v[w + 2] = old.z; acc.v[w + 3] = old.w;
+    }
+  }
+  const int longest = __reduce_max_sync(FULL, ge - b);
+  int next_j = 0;
+  float next_a = 0.f;
+  if (b + l < ge) {
+    const int x = a.ent ? ld_stream(a.ent + b + l) : b + l;
+    next_j = ld_stream(a.crd + x);
+    next_a = ld_stream(val + (a.val_compact ? b + l : x));
+  }
+#pragma unroll 1
+  for (int q0 = 0; q0 < longest; q0 += L) {
+    const int p0 = b + q0;
+    const int my_j = next_j;
+    const float my_a = next_a;
+    if (p0 + L + l < ge) {
+      const int x = a.ent ? ld_stream(a.ent + p0 + L + l) : p0 + L + l;
+      next_j = ld_stream(a.crd + x);
+      next_a = ld_stream(val + (a.val_compact ? p0 + L + l : x));
+    }
+    const int cnt = ge - p0;                    // entries this group still has (may be <= 0)
+    const int most = min(L, longest - q0);      // warp-uniform
+#pragma unroll 1
+    for (int t0 = 0; t0 < most; t0 += U) {
+      float av[U];
+      Pack<W> bv[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int t = t0 + u;
+        const unsigned j = (unsigned)__shfl_sync(FULL, my_j, t, L);
+        av[u] = __shfl_sync(FULL, my_a, t, L);
+        if (t < cnt && col_ok) {
+          bv[u] = ld_dense<W>(Bcol + (size_t)((unsigned long long)j * ldb));
+        } else {
+          av[u] = 0.f;
+#pragma unroll
+          for (int w = 0; w < W; w++) bv[u].v[w] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+#pragma unroll
+        for (int w = 0; w < W; w++) acc.v[w] = fmaf(av[u], bv[u].v[w], acc.v[w]);
+      }
+    }
+  }
+  if (mine && col_ok) st_stream<W>(crow + col0, epilogue<W>(acc, a.bias, col0, a.relu));
+  // rows too long for one lane group: the whole warp, one row after the other
+  if (__any_sync(FULL, by_warp)) {
+#pragma unroll 1
+    for (int gg = 0; gg < G; gg++) {
+      if (!__shfl_sync(FULL, (int)by_warp, gg * L)) continue;
+      const int rb = __shfl_sync(FULL, b, gg * L), re = __shfl_sync(FULL, e, gg * L);
+      Pack<W> acc2[1];
+      bool ok2[1] = {col_ok};
+#pragma unroll
+      for (int w = 0; w < W; w++) acc2[0].v[w] = 0.f;
+      float* crow2 = a.C + bz * a.stride_c + (long long)(row_base + gg) * a.ldc;
+      if (a.accumulate && lane < L && col_ok) {
+#pragma unroll
+        for (int w = 0; w < W; w += 4) {
+          const float4 old = *reinterpret_cast<const float4*>(crow2 + col0 + w);
+          acc2[0].v[w] = old.x; acc2[0].v[w + 1] = old.y; acc2[0].v[w + 2] = old.z; acc2[0].v[w + 3] = old.w;
+        }
+      }
+      accumulate_range<L, 1, W, EXACT>(acc2, a.crd, val, Bcol, ldb, rb, re, lane, ok2, a.ent,
+                                       a.val_compact != 0);
+      reduce_groups<L, 1, W>(acc2);
+      if (lane < L && col_ok) st_stream<W>(crow2 + col0, epilogue<W>(acc2[0], a.bias, col0, a.relu));
+    }
+  }
+}
+
+template <int L, int W, bool EXACT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
+spmm_rows_grouped_kernel(SpmmArgs a) {
+  rows_grouped_body<L, W, EXACT>(a, (int)blockIdx.x);
+}
+
 struct HeavyArgs {
   const int* hdr;
   const int* heavy_row;
   const int* heavy_seg0;
   const int* heavy_nseg;
   const int* seg_heavy;
-  float* scratch;            // [batch][segments_cap][k]
+  float* scratch;            // [batch][segments][k] segment sums of multi-segment rows
   long long scratch_batch;   // elements between batch items
+  int* arrived;              // [batch][column tiles][segments] segments done per heavy row (zeroed)
+  int segments;              // heavy CTAs in grid.x (>= the plan's segment count)
+  int first_heavy;           // blockIdx.x of the first heavy CTA; the row CTAs take the other indices
 };
 
-// One CTA per heavy-row segment; grid = (segments, column tiles, batch).
+// One CTA per heavy-row segment.  The CTA that finishes a row's last outstanding segment adds
+// the row's segment sums in segment order and writes the row (fixed order, whichever CTA does it).
 template <int L, int VEC, int W, bool EXACT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
-spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
+__device__ __forceinline__ void heavy_body(const SpmmArgs& a, const HeavyArgs& h, int seg) {
   constexpr int TILE = L * W * VEC;
   __shared__ Pack<W> part[kWarpsPerCta][VEC][L];
-  const int seg = blockIdx.x;
+  __shared__ int s_last;
   if (seg >= __ldg(h.hdr + 1)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = __ldg(h.seg_heavy + seg);
@@ -361,24 +493,25 @@ spmm_heavy_kernel(SpmmArgs a, HeavyArgs h) {
 #pragma unroll
         for (int w = 0; w < W; w += 4)
           *reinterpret_cast<float4*>(dst + w) = make_float4(s.v[w], s.v[w + 1], s.v[w + 2], s.v[w + 3]);
+        __threadfence();  // the segment sum is visible before this CTA counts itself done
       }
     }
   }
-}
-
-// Adds the segment sums of every multi-segment heavy row in segment order.
-// grid = (heavy rows bound, 1, batch); threads span the columns in float4 units.
-__global__ void spmm_heavy_finalize_kernel(SpmmArgs a, HeavyArgs h) {
-  const int slot = blockIdx.x;
-  if (slot >= __ldg(h.hdr)) return;
-  const int nseg = __ldg(h.heavy_nseg + slot);
   if (nseg == 1) return;
-  const int row = __ldg(h.heavy_row + slot);
-  const int seg0 = __ldg(h.heavy_seg0 + slot);
-  const long long bz = blockIdx.z;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* cnt = h.arrived + ((long long)bz * gridDim.y + blockIdx.y) * h.segments + seg0;
+    s_last = (atomicAdd(cnt, 1) == nseg - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
   const float* src = h.scratch + bz * h.scratch_batch + (long long)seg0 * a.k;
   float* crow = a.C + bz * a.stride_c + (long long)row * a.ldc;
-  for (int col = threadIdx.x * 4; col < a.k; col += blockDim.x * 4) {
+  const int tile0 = blockIdx.y * TILE;
+  for (int c = threadIdx.x * 4; c < TILE; c += blockDim.x * 4) {
+    const int col = tile0 + c;
+    if (col >= a.k) break;
     Pack<4> s;
     s.v[0] = s.v[1] = s.v[2] = s.v[3] = 0.f;
     if (a.accumulate) {
@@ -386,11 +519,36 @@ __global__ void spmm_heavy_finalize_kernel(SpmmArgs a, HeavyArgs h) {
       s.v[0] = old.x; s.v[1] = old.y; s.v[2] = old.z; s.v[3] = old.w;
     }
     for (int t = 0; t < nseg; t++) {
-      const float4 v = *reinterpret_cast<const float4*>(src + (long long)t * a.k + col);
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (long long)t * a.k + col));
       s.v[0] += v.x; s.v[1] += v.y; s.v[2] += v.z; s.v[3] += v.w;
     }
     st_stream<4>(crow + col, epilogue<4>(s, a.bias, col, a.relu));
   }
+}
+
+// Rows and heavy-row segments in one launch; grid = (row blocks + segments, column tiles, batch):
+// the segment CTAs [first_heavy, first_heavy + segments) run beside the row CTAs instead of
+// waiting for a launch of their own.
+// (Both bodies inlined want 76-96 registers; three CTAs per SM, like the rows kernel alone gets,
+// caps that at 85.)
+template <int L, int VEC, int W, bool EXACT, int R>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, R > 1 ? 4 : 3)
+spmm_rows_heavy_kernel(SpmmArgs a, HeavyArgs h) {
+  const int hb = (int)blockIdx.x - h.first_heavy;
+  if (hb >= 0 && hb < h.segments)
+    heavy_body<L, VEC, W, EXACT>(a, h, hb);
+  else
+    rows_body<L, VEC, W, EXACT, R>(a, hb < 0 ? (int)blockIdx.x : hb - h.segments + h.first_heavy);
+}
+
+template <int L, int W, bool EXACT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
+spmm_grouped_heavy_kernel(SpmmArgs a, HeavyArgs h) {
+  const int hb = (int)blockIdx.x - h.first_heavy;
+  if (hb >= 0 && hb < h.segments)
+    heavy_body<L, 1, W, EXACT>(a, h, hb);
+  else
+    rows_grouped_body<L, W, EXACT>(a, hb < 0 ? (int)blockIdx.x : hb - h.segments + h.first_heavy);
 }
 
 // Scalar path for any dtype / any layout: one warp per row, lanes span 32 columns per grid.y
@@ -423,28 +581,51 @@ static int launch_vec2(const SpmmArgs& a, int64_t batch, const void* plan, int64
                        int64_t plan_segments, void* scratch, cudaStream_t st) {
   constexpr int TILE = L * W * VEC;
   const unsigned tiles = (unsigned)ceil_div(a.k, TILE);
-  if (a.short_rows) {
-    dim3 grid((unsigned)ceil_div(ceil_div(a.m, kShortRowsPerWarp), kWarpsPerCta), tiles, (unsigned)batch);
-    spmm_rows_kernel<L, VEC, W, EXACT, kShortRowsPerWarp><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
-  } else {
-    dim3 grid((unsigned)ceil_div(a.m, kWarpsPerCta), tiles, (unsigned)batch);
-    spmm_rows_kernel<L, VEC, W, EXACT, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
-  }
-  SB_LAUNCH_CHECK("spmm_rows_kernel");
+  // short rows: a row per lane group where the tile is narrow, else several rows per warp
+  constexpr bool kGrouped = (L <= 16 && VEC == 1);
+  const int rows_per_warp = !a.short_rows ? 1 : (kGrouped ? 32 / L : kShortRowsPerWarp);
+  const int64_t row_ctas = ceil_div(ceil_div(a.m, rows_per_warp), kWarpsPerCta);
   if (plan && plan_segments != 0) {
     PlanView pv = plan_view(plan, nnz);
     const int64_t segs = plan_segments < 0 ? pv.cap_seg : plan_segments;
+    float* sums = static_cast<float*>(scratch);
+    int* arrived = reinterpret_cast<int*>(sums + (size_t)segs * a.k * batch);
     HeavyArgs h{pv.hdr, pv.heavy_row, pv.heavy_seg0, pv.heavy_nseg, pv.seg_heavy,
-                static_cast<float*>(scratch), (long long)segs * a.k};
-    dim3 hg((unsigned)segs, tiles, (unsigned)batch);
-    spmm_heavy_kernel<L, VEC, W, EXACT><<<hg, kWarpsPerCta * 32, 0, st>>>(a, h);
-    SB_LAUNCH_CHECK("spmm_heavy_kernel");
-    const int64_t heavy_bound = segs < pv.cap_heavy ? segs : pv.cap_heavy;
-    dim3 fg((unsigned)heavy_bound, 1, (unsigned)batch);
-    const int threads = a.k >= 1024 ? 256 : (a.k >= 512 ? 128 : 64);
-    spmm_heavy_finalize_kernel<<<fg, threads, 0, st>>>(a, h);
-    SB_LAUNCH_CHECK("spmm_heavy_finalize_kernel");
+                sums, (long long)segs * a.k, arrived, (int)segs, 0};
+    SB_CUDA(cudaMemsetAsync(arrived, 0, (size_t)segs * tiles * batch * sizeof(int), st));
+    // Long rows: the rows in a launch of their own, then the segments (one launch with both
+    // bodies needs 10-20 more registers per thread and measured 3 % / 20 % slower at 256 / 64
+    // columns on a 2 M-row power-law graph).  Short-row passes (a row chunk's share of a
+    // matrix: few segments, a launch of their own would leave most SMs idle): one launch, the
+    // segment CTAs behind the row CTAs (4 % faster than in front at 256 columns).
+    int64_t fused_rows = row_ctas;
+    if (!a.short_rows) {
+      dim3 rgrid((unsigned)row_ctas, tiles, (unsigned)batch);
+      spmm_rows_kernel<L, VEC, W, EXACT, 1><<<rgrid, kWarpsPerCta * 32, 0, st>>>(a);
+      SB_LAUNCH_CHECK("spmm_rows_kernel");
+      fused_rows = 0;
+    }
+    h.first_heavy = (int)fused_rows;
+    dim3 grid((unsigned)(segs + fused_rows), tiles, (unsigned)batch);
+    if (a.short_rows) {
+      if constexpr (kGrouped)
+        spmm_grouped_heavy_kernel<L, W, EXACT><<<grid, kWarpsPerCta * 32, 0, st>>>(a, h);
+      else
+        spmm_rows_heavy_kernel<L, VEC, W, EXACT, kShortRowsPerWarp><<<grid, kWarpsPerCta * 32, 0, st>>>(a, h);
+    } else
+      spmm_rows_heavy_kernel<L, VEC, W, EXACT, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(a, h);
+    SB_LAUNCH_CHECK("spmm_rows_heavy_kernel");
+    return SB_OK;
   }
+  dim3 grid((unsigned)row_ctas, tiles, (unsigned)batch);
+  if (a.short_rows) {
+    if constexpr (kGrouped)
+      spmm_rows_grouped_kernel<L, W, EXACT><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+    else
+      spmm_rows_kernel<L, VEC, W, EXACT, kShortRowsPerWarp><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  } else
+    spmm_rows_kernel<L, VEC, W, EXACT, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+  SB_LAUNCH_CHECK("spmm_rows_kernel");
   return SB_OK;
 }
 
@@ -535,7 +716,9 @@ extern "C" {
 
 size_t sb_spmm_csr_scratch_bytes(int64_t segments, int64_t k, int64_t batch) {
   if (segments <= 0 || k <= 0 || batch <= 0) return 0;
-  return (size_t)segments * (size_t)k * (size_t)batch * sizeof(float);
+  // segment sums + one arrival counter per (segment, column tile of at most 256 columns)
+  const size_t tiles = (size_t)ceil_div(k, 16);
+  return (size_t)segments * (size_t)batch * ((size_t)k * sizeof(float) + tiles * sizeof(int));
 }
 
 static int spmm_csr_f32_impl(int64_t m, int64_t n, int64_t k, int64_t nnz, const int32_t* pos,

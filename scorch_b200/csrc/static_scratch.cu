@@ -29,7 +29,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[SB_STATIC_SCRATC
 static std::mutex g_mu;
 static unsigned char* g_dev_ptr[64] = {nullptr};
 
-// Device address of the array on the current device; resolved on the first call per device.
+// Device address of the array on the current device; resolved on the first call per device and
+// kept for the life of the process (a cudaDeviceReset would leave it stale: see the header).
 static int static_scratch_ptr(unsigned char** out) {
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
@@ -56,12 +57,13 @@ extern "C" {
 int sb_spmv_csr_f32_static(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
                            const int32_t* crd, const float* val, const float* x, float* y,
                            void* stream) {
+  SB_CHECK_ARG(m >= 0 && n >= 0 && nnz >= 0, "spmv_static: negative size");
+  SB_CHECK_ARG(pos, "spmv_static: pos is null");
   if (nnz > kStaticMaxNnz)
     return fail(SB_ERR_UNSUPPORTED,
                 "spmv_static: nnz=%lld exceeds the %lld entries the built-in scratch covers; use "
-                "sb_spmv_csr_f32 with caller-provided plan and scratch",
+                "sb_spmv_csr_f32 with a scratch buffer of your own",
                 (long long)nnz, (long long)kStaticMaxNnz);
-  SB_CHECK_ARG(m >= 0 && nnz >= 0 && pos, "spmv_static: bad size or null pos");
   unsigned char* base = nullptr;
   int rc = static_scratch_ptr(&base);
   if (rc != SB_OK) return rc;

@@ -249,6 +249,8 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
         if bias.numel() != k:
             raise ValueError("bias must have k elements")
     shape = (batch, m, k) if batched else (m, k)
+    if accumulate and out is None:
+        raise ValueError("accumulate needs the tensor to add to (out=)")
     if out is None:
         out = torch.empty(shape, dtype=torch.float32, device=B.device)
         ldc = k
@@ -263,8 +265,6 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
             if out.stride(1) != 1 or out.stride(0) < k:
                 raise ValueError("out rows must be contiguous")
             ldc = out.stride(0)
-    if accumulate and out is None:
-        raise ValueError("accumulate needs the tensor to add to (out=)")
     if plan is None:
         plan = plan_for(pos, nnz)
     L = _lib.lib()

@@ -349,6 +349,7 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
     Exposed communication is one chunk's transform + gather at the start of each layer.  With one
     rank and one chunk every layer is a single full-width SpMM."""
     spmm_fn = spmm_fn or _default_spmm
+    lookahead = int(os.environ.get("SCORCH_B200_GCN_LOOKAHEAD", lookahead))
     dev = x_local.device
     k1, k2 = W1.shape[1], W2.shape[1]
     g = _Gatherer(shard, dev, group, timeline)

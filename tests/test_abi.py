@@ -35,7 +35,8 @@ def test_size_queries_are_pure_host_functions(sb_lib):
     assert sb_lib.sb_csr_plan_bytes(10, 0) >= 32
     nnz = 10 * HEAVY_ROW_NNZ
     assert sb_lib.sb_csr_plan_max_segments(nnz) >= 10
-    assert sb_lib.sb_spmm_csr_scratch_bytes(7, 64, 2) == 7 * 64 * 2 * 4
+    # segment sums (k floats) + arrival counters (one per 16 columns) per segment and batch item
+    assert sb_lib.sb_spmm_csr_scratch_bytes(7, 64, 2) == 7 * 2 * (64 * 4 + 4 * 4)
     assert sb_lib.sb_spmm_csr_scratch_bytes(0, 64, 1) == 0
     assert sb_lib.sb_spmv_csr_scratch_bytes(0) == 0
     assert sb_lib.sb_spmv_csr_scratch_bytes(5000) == 3 * 256  # 3 tiles -> three padded arrays

@@ -99,6 +99,38 @@ def test_spmm_vs_oracle_all_column_widths(oracle, k):
     assert_close(oracle, got, oracle.spmm_csr_acc64(pos, crd, val, B, bias, True), f"k={k} bias+relu")
 
 
+@pytest.mark.parametrize("k", [8, 16, 20, 32, 64, 72, 128, 256, 300])
+def test_spmm_many_short_rows(oracle, k):
+    """Mean row length below the short-row threshold: a row per lane group (narrow tiles) or
+    several rows per warp; rows too long for a lane group, empty rows and heavy rows mixed in,
+    plain and accumulating, with and without the heavy-row plan."""
+    from scorch_b200 import kernels as K
+    from scorch_b200._lib import HEAVY_ROW_NNZ as T
+    rng = np.random.default_rng(100 + k)
+    m, n = 1003, 4000
+    lens = rng.poisson(9, size=m)
+    lens[rng.integers(0, m, 25)] = 0
+    lens[[3, 40, 41, 500, 1002]] = [65, 300, 64, 1024, 97]
+    lens[[7, 600]] = [T + 9, 2 * T + 100]
+    pos, crd, val = random_csr(m, n, lens, seed=200 + k)
+    assert len(crd) < 24 * m
+    val = (val / np.sqrt(np.repeat(np.maximum(lens, 1), lens))).astype(np.float32)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    bias = rng.standard_normal(k).astype(np.float32)
+    C0 = rng.standard_normal((m, k)).astype(np.float32)
+    dpos, dcrd, dval, dB = dev(pos), dev(crd), dev(val), dev(B)
+    want = oracle.spmm_csr_acc64(pos, crd, val, B)
+    plan = K.CsrPlan(dpos, len(crd))
+    assert plan.segments == 2 + 3
+    got = K.spmm_csr(dpos, dcrd, dval, dB, plan=plan)
+    assert_close(oracle, got, want, f"short rows k={k}")
+    assert torch.equal(got, K.spmm_csr(dpos, dcrd, dval, dB, plan=plan))
+    got = K.spmm_csr(dpos, dcrd, dval, dB, bias=dev(bias), relu=True, plan=plan, out=dev(C0.copy()),
+                     accumulate=k % 4 == 0)
+    w2 = want + bias.astype(np.float64) + (C0.astype(np.float64) if k % 4 == 0 else 0)
+    assert_close(oracle, got, np.maximum(w2, 0), f"short rows k={k} epilogue")
+
+
 @pytest.mark.parametrize("k", [64, 256, 520])
 def test_spmm_heavy_rows_and_plan(oracle, k):
     """Rows around and far above the heavy threshold go through the segment kernels."""

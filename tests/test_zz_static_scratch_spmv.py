@@ -1,10 +1,11 @@
 """The allocation-free SpMV entry point (sb_spmv_csr_f32_static) against the regular one.
 
-Who needs it: code that runs on a GPU it does not own the memory of — a plugin inside another
+Who needs it: code that runs on a GPU whose memory it does not own — a plugin inside another
 runtime's arena, a service that may not touch the allocator once it is up — cannot hand the
-library a plan buffer or scratch, and cannot let it call cudaMalloc either.  The static entry
-keeps both inside the library image.  This file is collected last on purpose: if it fails, a run
-that stops at the first failure has already been through every other test.
+library a scratch buffer for the partial sums of rows cut by tile borders, and cannot let it call
+cudaMalloc either.  The static entry keeps that scratch in an array inside the library image,
+shared by all calls: the tests run different matrices back to back to show that nothing a call
+leaves in the array reaches the next one.
 """
 from __future__ import annotations
 
@@ -42,7 +43,7 @@ def _static_spmv(pos, crd, val, x):
 def test_static_spmv_matches_regular_entry_on_two_calls_in_a_row():
     from scorch_b200 import kernels as K
     from scorch_b200._lib import HEAVY_ROW_NNZ as T
-    # first call: many heavy rows, so the shared array is left full of plan entries and sums
+    # first call: many rows cut by tile borders, so the shared array is left full of partial sums
     lens1 = np.random.default_rng(0).poisson(10, size=4000)
     lens1[[3, 900, 901, 3999]] = [6 * T + 5, T + 1, 2 * T, 3 * T - 7]
     a1 = _matrix(4000, 20000, lens1, seed=1)
@@ -52,18 +53,25 @@ def test_static_spmv_matches_regular_entry_on_two_calls_in_a_row():
     lens2[-1] = 0
     a2 = _matrix(1500, 9000, lens2, seed=3)
 
-    want1, want2 = K.spmv_csr(*a1), K.spmv_csr(*a2)
+    # third matrix: thousands of empty rows (more than a tile's worth of entries would span)
+    # between two rows that tile borders cut, and empty rows at both ends
+    lens3 = np.zeros(9000, np.int64)
+    lens3[[5, 6, 8000, 8001]] = [3000, 2500, 4100, 7]
+    a3 = _matrix(9000, 30000, lens3, seed=5)
+
+    want1, want2, want3 = K.spmv_csr(*a1), K.spmv_csr(*a2), K.spmv_csr(*a3)
     got1 = _static_spmv(*a1)
     torch.cuda.synchronize()
     free_before = torch.cuda.mem_get_info()[0]
     got2 = _static_spmv(*a2)
+    got3 = _static_spmv(*a3)
     got1_again = _static_spmv(*a1)
     torch.cuda.synchronize()
     # nothing was allocated by the calls themselves (y comes from torch's cached pool)
     assert torch.cuda.mem_get_info()[0] == free_before
     # same kernels, same fixed-order sums: the results agree to the last bit, and well inside
     # the suite's tolerance
-    for got, want in ((got1, want1), (got2, want2), (got1_again, want1)):
+    for got, want in ((got1, want1), (got2, want2), (got3, want3), (got1_again, want1)):
         assert torch.isfinite(got).all()
         torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
         assert torch.equal(got, want)
@@ -76,3 +84,7 @@ def test_static_spmv_rejects_sizes_beyond_the_builtin_scratch():
     rc = L.sb_spmv_csr_f32_static(2, 2, _lib.STATIC_SPMV_MAX_NNZ + 1, one.data_ptr(), one.data_ptr(),
                                   one.data_ptr(), one.data_ptr(), one.data_ptr(), None)
     assert rc == 5 and b"exceeds" in L.sb_last_error()
+    # argument errors are reported as such, whatever the size
+    rc = L.sb_spmv_csr_f32_static(2, 2, _lib.STATIC_SPMV_MAX_NNZ + 1, None, one.data_ptr(),
+                                  one.data_ptr(), one.data_ptr(), one.data_ptr(), None)
+    assert rc == 1 and b"pos is null" in L.sb_last_error()
