@@ -317,6 +317,27 @@ SB_API int sb_dense_to_csr_count(int64_t m, int64_t n, const float* A, int64_t l
                                  int64_t* nnz_host, void* ws, size_t ws_bytes, void* stream);
 SB_API int sb_dense_to_csr_fill(int64_t m, int64_t n, const float* A, int64_t lda,
                                 const int32_t* pos, int32_t* crd, float* val, void* stream);
+/* CSR transpose: (tpos, tcrd, tval) = CSR of the transpose of the m x n matrix (pos, crd, val), i.e.
+ * its CSC form; output rows hold their entries in ascending source-row order.  `val` / `tval` may
+ * both be NULL (pattern only); otherwise `dtype` (SB_F32 ... SB_I64) gives their element type.
+ * `ws`: sb_csr_transpose_workspace_bytes(n, nnz) bytes, 16-byte aligned.  Asynchronous.
+ * Replaces: the torch-op fast path of STensor.change_mode_order for 2-D compressed operands,
+ *           src/scorch/stensor.py:785-896, which runs before every prebuilt dispatch on an operand
+ *           stored in the other mode order (src/scorch/ops.py:299-303,333-346). */
+SB_API size_t sb_csr_transpose_workspace_bytes(int64_t n, int64_t nnz);
+SB_API int sb_csr_transpose(int dtype, int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                            const int32_t* crd, const void* val, int32_t* tpos, int32_t* tcrd,
+                            void* tval, void* ws, size_t ws_bytes, void* stream);
+
+/* Per-row top-k of a dense row-major fp32 matrix, written as CSR with exactly k entries per row:
+ * pos[i] = i*k, the columns of the k largest values of row i in ascending order (ties between
+ * equal values go to the lower column), val = the kept values, clamped at zero when `relu` is
+ * set.  This is how the activations of benchmark configuration 3 are defined (a sparse
+ * autoencoder keeps the k largest pre-activations per sample); the reference itself has no such
+ * operator, its callers build CSR operands with torch (bench/bench_sparse_autoencoder.py:233,261). */
+SB_API int sb_topk_rows_to_csr_f32(int64_t m, int64_t n, int64_t k, const float* X, int64_t ldx,
+                                   int relu, int32_t* pos, int32_t* crd, float* val, void* stream);
+
 SB_API int sb_csr_sym_normalize_f32(int64_t m, int64_t nnz, const int32_t* pos, const int32_t* crd,
                                     float* val, void* stream);
 

@@ -14,12 +14,21 @@ machine and run on another:
 * ``x86-64-v4``  (AVX-512 F/BW/..) -> ``oracle/_ref/x86-64-v4/scorch_ops.so``
 
 ``oracle/ref_loader.py`` picks the widest level the running host supports.
+
+The reference's Python package (``src/scorch``, pure Python) is staged beside the binaries as
+``oracle/_ref/pkg/src/scorch`` so that tests can run the reference's own ``scorch.matmul`` /
+``scorch.einsum`` front end — once over the reference's kernels (the stock CPU path) and once
+over this repository's drop-in ``scorch_ops`` module.
 Outputs go only into ``oracle/_ref/`` (git-ignored).
+
+The reference checkout is found through ``SCORCH_REFERENCE_ROOT``; without it a directory
+named ``reference`` beside this repository is tried.
 """
 from __future__ import annotations
 
 import glob
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -30,7 +39,36 @@ LEVELS = ("x86-64-v3", "x86-64-v4")
 
 
 def reference_root() -> str:
-    return os.environ.get("SCORCH_REFERENCE_ROOT", "/root/reference")
+    env = os.environ.get("SCORCH_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def stage_python_package(root: str, verbose: bool = True) -> str | None:
+    """Copy the reference's pure-Python package (and the C++ headers its JIT path prepends) to
+    oracle/_ref/pkg, laid out like the reference project: the package finds its project root by
+    walking up to the first directory that holds a ``setup.py``."""
+    pkg = os.path.join(root, "src", "scorch")
+    if not os.path.isdir(pkg):
+        return None
+    base = os.path.join(OUT, "pkg")
+    dst = os.path.join(base, "src", "scorch")
+    newest = max(os.path.getmtime(os.path.join(d, f)) for d, _, fs in os.walk(pkg) for f in fs
+                 if f.endswith(".py"))
+    stamp = os.path.join(base, ".staged")
+    if os.path.exists(stamp) and os.path.getmtime(stamp) >= newest and os.path.isdir(dst):
+        return dst
+    shutil.rmtree(base, ignore_errors=True)
+    shutil.copytree(pkg, dst, ignore=shutil.ignore_patterns("__pycache__", "*.so", "*.pyc"))
+    if os.path.isdir(os.path.join(root, "csrc")):
+        shutil.copytree(os.path.join(root, "csrc"), os.path.join(base, "csrc"))
+    with open(os.path.join(base, "setup.py"), "w") as f:
+        f.write("# marks the project root for the staged package (it walks up to a setup.py)\n")
+    open(stamp, "w").close()
+    if verbose:
+        print(f"[oracle/_ref] staged the reference's Python package at {dst}")
+    return dst
 
 
 def build(force: bool = False, verbose: bool = True) -> list[str]:
@@ -39,6 +77,7 @@ def build(force: bool = False, verbose: bool = True) -> list[str]:
         if verbose:
             print(f"[oracle/_ref] reference source not found at {src}: keeping prebuilt files")
         return []
+    stage_python_package(reference_root(), verbose)
     import torch
     from torch.utils import cpp_extension as cx
     import pybind11

@@ -225,3 +225,33 @@ def allclose_report(got, want64, rtol=1e-4, atol=1e-5):
     bad = err > (atol + rtol * np.abs(want64))
     ok = (not bad.any()) and bool(np.isfinite(got).all())
     return ok, (float(err.max()) if err.size else 0.0), int(bad.sum())
+
+
+def csr_transpose(pos, crd, val, n):
+    """CSR of the transpose (= CSC of the matrix), rows in ascending source-row order: what the
+    torch-op fast path of STensor.change_mode_order produces for a 2-D compressed operand
+    (src/scorch/stensor.py:785-896: argsort of new_row * cols + new_col, bincount, cumsum)."""
+    pos, crd = np.asarray(pos, np.int64), np.asarray(crd, np.int64)
+    m = len(pos) - 1
+    row = np.repeat(np.arange(m, dtype=np.int64), np.diff(pos))
+    order = np.argsort(crd * max(m, 1) + row, kind="stable")
+    tpos = np.concatenate([[0], np.cumsum(np.bincount(crd, minlength=n))]).astype(np.int32)
+    tval = None if val is None else np.asarray(val)[order]
+    return tpos, row[order].astype(np.int32), tval
+
+
+def topk_rows_to_csr(X, k, relu=False):
+    """Exactly k entries per row: the k largest values of each row (ties between equal values go
+    to the lower column), columns ascending, values clamped at zero when `relu` is set — the
+    activation rule of benchmark configuration 3 (top-k of the pre-activations, ReLU'd)."""
+    X = np.asarray(X, np.float32)
+    m, n = X.shape
+    crd = np.empty((m, k), np.int32)
+    val = np.empty((m, k), np.float32)
+    cols = np.arange(n)
+    for i in range(m):
+        pick = np.sort(np.lexsort((cols, -X[i].astype(np.float64)))[:k])
+        crd[i] = pick
+        val[i] = np.maximum(X[i, pick], 0) if relu else X[i, pick]
+    pos = (np.arange(m + 1) * k).astype(np.int32)
+    return pos, crd.reshape(-1), val.reshape(-1)

@@ -54,3 +54,10 @@ def load():
 
 def level() -> str | None:
     return _level
+
+
+def reference_package_dir() -> str | None:
+    """Directory to put on sys.path to import the reference's own Python package ``scorch``
+    (staged by ``oracle/build_ref.py``), or None when it has not been staged."""
+    d = os.path.join(_HERE, "_ref", "pkg", "src")
+    return d if os.path.isdir(os.path.join(d, "scorch")) else None

@@ -68,6 +68,9 @@ SIGNATURES = {
     "sb_dense_to_csr_workspace_bytes": (_sz, [_i64]),
     "sb_dense_to_csr_count": (_int, [_i64, _i64, _ptr, _i64, _ptr, C.POINTER(_i64), _ptr, _sz, _ptr]),
     "sb_dense_to_csr_fill": (_int, [_i64, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _ptr]),
+    "sb_csr_transpose_workspace_bytes": (_sz, [_i64, _i64]),
+    "sb_csr_transpose": (_int, [_int, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _ptr]),
+    "sb_topk_rows_to_csr_f32": (_int, [_i64, _i64, _i64, _ptr, _i64, _int, _ptr, _ptr, _ptr, _ptr]),
     "sb_csr_sym_normalize_f32": (_int, [_i64, _i64, _ptr, _ptr, _ptr, _ptr]),
     "sb_coo_rows_to_csr_pos": (_int, [_i64, _i64, _ptr, _ptr, _ptr]),
     "sb_csr_pos_to_coo_rows": (_int, [_i64, _i64, _ptr, _ptr, _ptr]),

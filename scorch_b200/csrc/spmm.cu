@@ -642,6 +642,10 @@ static int launch_generic(int64_t m, int64_t k, const int32_t* pos, const int32_
                           const T* val, const T* B, int64_t ldb, const T* bias, int relu, T* C,
                           int64_t ldc, int64_t batch, int64_t sv, int64_t sbb, int64_t sc,
                           cudaStream_t st) {
+  if (ceil_div(k, 32) > 65535)
+    return fail(SB_ERR_UNSUPPORTED,
+                "spmm: the scalar path (dtype other than f32, or unaligned operands) takes at most "
+                "%d columns, got %lld", 65535 * 32, (long long)k);
   dim3 grid((unsigned)ceil_div(m, kWarpsPerCta), (unsigned)ceil_div(k, 32), (unsigned)batch);
   spmm_generic_kernel<T><<<grid, kWarpsPerCta * 32, 0, st>>>(
       (int)m, (int)k, pos, crd, val, B, ldb, bias, relu, C, ldc, sv, sbb, sc);

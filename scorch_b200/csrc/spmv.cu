@@ -168,7 +168,9 @@ static int check_spmv(int64_t m, int64_t n, int64_t nnz, const void* pos, const 
                       const void* val, const void* x, const void* y) {
   SB_CHECK_ARG(m >= 0 && n >= 0 && nnz >= 0, "spmv: negative size");
   SB_CHECK_ARG(m < INT32_MAX / 32 * 32 && n < INT32_MAX, "spmv: dimension exceeds int32");
-  if (nnz > INT32_MAX) return fail(SB_ERR_OVERFLOW, "spmv: nnz does not fit int32 row pointers");
+  // (the tile kernels add up to one tile, 2048 entries, to an entry index held in an int)
+  if (nnz > INT32_MAX - 4096)
+    return fail(SB_ERR_OVERFLOW, "spmv: nnz=%lld does not fit int32 row pointers", (long long)nnz);
   SB_CHECK_ARG(pos, "spmv: pos is null");
   SB_CHECK_ARG(nnz == 0 || (crd && val && x), "spmv: null crd/val/x");
   SB_CHECK_ARG(m == 0 || y, "spmv: y is null");

@@ -33,6 +33,14 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _wrote(t: torch.Tensor) -> torch.Tensor:
+    """The library has written `t` through its raw pointer: bump the tensor's version counter, as
+    a torch in-place op would, so that whatever is cached against the tensor's version (row
+    plans, the all-ones verdict of a mask) is not reused for the new contents."""
+    torch.autograd.graph.increment_version(t)
+    return t
+
+
 class CsrPlan:
     """Heavy-row plan of one CSR matrix (depends on ``pos`` only); see include/scorch_b200.h."""
 
@@ -201,7 +209,7 @@ def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
                                             float(scale), out.data_ptr(), d, batch, m * d, n * d, n * d,
                                             m * d, attn_plan.buf.data_ptr(), attn_plan.blocks,
                                             attn_plan.rem_nnz, _ptr(scratch), sbytes, int(stages), _stream()))
-    return out
+    return _wrote(out)
 
 
 BLOCKED_MIN_DENSE_FRACTION = 0.5   # below this the gather kernels alone are used
@@ -276,7 +284,7 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
                                             _ptr(bias), int(bool(relu)), out.data_ptr(), ldc, batch,
                                             stride_val, nb * k, m * k, block_plan.buf.data_ptr(),
                                             block_plan.blocks, block_plan.rem_nnz, _stream()))
-        return out
+        return _wrote(out)
     sbytes = L.sb_spmm_csr_scratch_bytes(plan.segments, k, batch)
     scratch = plan.scratch(sbytes) if sbytes else None
     with torch.cuda.device(B.device):
@@ -285,7 +293,7 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
                  val.data_ptr(), B.data_ptr(), ldb, _ptr(bias), int(bool(relu)),
                  out.data_ptr(), ldc, batch, stride_val, nb * k, m * k,
                  plan.buf.data_ptr(), plan.segments, _ptr(scratch), sbytes, _stream()))
-    return out
+    return _wrote(out)
 
 
 def _spmm_typed(pos, crd, val, B, n):
@@ -363,7 +371,7 @@ def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
                 m, K.shape[-2], d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val), Q.data_ptr(), d,
                 K.data_ptr(), d, out.data_ptr(), batch, Q.shape[-2] * d, K.shape[-2] * d, nnz,
                 block_plan.buf.data_ptr(), block_plan.blocks, block_plan.rem_nnz, _stream()))
-        return out
+        return _wrote(out)
     row = col = None
     if want_coords:
         row = torch.empty(nnz, dtype=torch.int32, device=Q.device)
@@ -373,6 +381,7 @@ def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
                                           _ptr(mask_val), Q.data_ptr(), d, K.data_ptr(), d,
                                           out.data_ptr(), _ptr(row), _ptr(col), batch,
                                           Q.shape[-2] * d, K.shape[-2] * d, nnz, _stream()))
+    _wrote(out)
     return (out, row, col) if want_coords else out
 
 
@@ -403,7 +412,7 @@ def csr_row_softmax(pos, val, scale: float = 1.0, out: Optional[torch.Tensor] = 
     with torch.cuda.device(val.device):
         check(_lib.lib().sb_csr_row_softmax_f32(m, nnz, pos.data_ptr(), val.data_ptr(),
                                                 out.data_ptr(), float(scale), batch, nnz, _stream()))
-    return out
+    return _wrote(out)
 
 
 def spgemm_csr(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n: int, timings: Optional[dict] = None
@@ -507,3 +516,52 @@ def csr_sym_normalize(pos: torch.Tensor, crd: torch.Tensor) -> torch.Tensor:
         check(_lib.lib().sb_csr_sym_normalize_f32(pos.numel() - 1, crd.numel(), pos.data_ptr(),
                                                   crd.data_ptr(), val.data_ptr(), _stream()))
     return val
+
+
+def csr_transpose(pos: torch.Tensor, crd: torch.Tensor, val: Optional[torch.Tensor], n: int):
+    """(tpos, tcrd, tval) of the transpose of the (m x n) CSR matrix (pos, crd, val): its CSC form,
+    output rows in ascending source-row order.  ``val`` may be None (pattern only).  What the
+    reference's front end does with torch ops for an operand stored in the other mode order
+    (src/scorch/stensor.py:785-896)."""
+    pos = _dev(pos, torch.int32, "pos")
+    crd = _dev(crd, torch.int32, "crd")
+    m, nnz = pos.numel() - 1, crd.numel()
+    code = SB_F32
+    if val is not None:
+        code = _DTYPE_CODE.get(val.dtype)
+        if code is None:
+            raise TypeError(f"unsupported value dtype {val.dtype}")
+        val = _dev(val, val.dtype, "val")
+        if val.numel() != nnz:
+            raise ValueError("val and crd differ in length")
+    L = _lib.lib()
+    dev = crd.device
+    tpos = torch.empty(n + 1, dtype=torch.int32, device=dev)
+    tcrd = torch.empty(nnz, dtype=torch.int32, device=dev)
+    tval = None if val is None else torch.empty_like(val)
+    wbytes = L.sb_csr_transpose_workspace_bytes(n, nnz)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(L.sb_csr_transpose(code, m, n, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(val),
+                                 tpos.data_ptr(), tcrd.data_ptr(), _ptr(tval), ws.data_ptr(), wbytes,
+                                 _stream()))
+    return tpos, tcrd, tval
+
+
+def topk_rows_to_csr(X: torch.Tensor, k: int, relu: bool = False):
+    """(pos, crd, val) with exactly k entries per row: the k largest values of each row of the
+    dense float32 matrix ``X``, columns ascending (ties go to the lower column), values clamped at
+    zero with ``relu`` — the activations of a top-k sparse autoencoder, ready for ``spmm_csr``."""
+    X = _row_major_2d(_dev(X, torch.float32, "X"), "X")
+    if X.dim() != 2:
+        raise ValueError("X must be 2-D")
+    m, n = X.shape
+    if not 0 <= k <= n:
+        raise ValueError("k must be in [0, columns]")
+    pos = torch.empty(m + 1, dtype=torch.int32, device=X.device)
+    crd = torch.empty(m * k, dtype=torch.int32, device=X.device)
+    val = torch.empty(m * k, dtype=torch.float32, device=X.device)
+    with torch.cuda.device(X.device):
+        check(_lib.lib().sb_topk_rows_to_csr_f32(m, n, k, X.data_ptr(), X.stride(0), int(bool(relu)),
+                                                 pos.data_ptr(), crd.data_ptr(), val.data_ptr(), _stream()))
+    return pos, crd, val

@@ -143,10 +143,13 @@ def matmul(a: Union[torch.Tensor, STensor], b: Union[torch.Tensor, STensor], **k
         raise NotImplementedError("sparse output of a dense x dense product needs the reference's "
                                   "compiler, which this package does not contain")
 
-    for t in (a, b):
-        if not t.format.is_dense() and t.index.mode_order != list(range(t.dim())):
-            raise NotImplementedError("operands with a non-default mode order must be re-laid-out "
-                                      "first (reference: STensor.change_mode_order)")
+    # sparse 2-D operands stored in the other mode order are re-laid-out to the canonical one
+    # before dispatch, on the device (reference: src/scorch/ops.py:299-303,333-346)
+    if a.dim() == 2 and not a.format.is_dense() and a.index.mode_order != [0, 1]:
+        a = a.copy().change_mode_order([0, 1])
+    if b.dim() == 2 and a.dim() == 2 and b.index.mode_order != [0, 1] and not (
+            a.format.is_dense() and b.format.is_dense()):
+        b = b.copy().change_mode_order([0, 1])
 
     resolved = resolve_prebuilt_matmul(a, b, output_format=requested)
     if resolved is None:

@@ -127,6 +127,49 @@ class STensor:
     def cpu(self) -> "STensor":
         return self.to("cpu")
 
+    def change_mode_order(self, mode_order: List[int]) -> "STensor":
+        """Re-lay-out a 2-D tensor so that its physical axes follow ``mode_order`` (reference:
+        STensor.change_mode_order, stensor.py:740-896; ``mode_order[p]`` is the logical axis that
+        physical axis ``p`` stores).  In place, returns self.  Dense tensors are permuted with
+        torch; compressed (``d,s``) and coordinate (``o,o``) tensors go through the device
+        transpose kernel (host tensors are moved to the GPU for it and back)."""
+        dim = self.dim()
+        if sorted(mode_order) != list(range(dim)):
+            raise AssertionError("mode_order must be a permutation")
+        old = list(self.index.mode_order)
+        if old == list(mode_order):
+            return self
+        if dim != 2:
+            raise NotImplementedError("mode-order changes are implemented for 2-D tensors")
+        # the only other 2-D order is the transpose of the stored arrays
+        rows, cols = self.shape
+        f = str(self.format)
+        if f == "d,d":
+            values = self.values.reshape(rows, cols).t().contiguous().reshape(-1)
+            mode_indices = [[], []]
+        elif f in ("d,s", "o,o"):
+            from . import kernels as K
+            on_host = not self.values.is_cuda
+            dev = torch.device("cuda", torch.cuda.current_device()) if on_host else self.values.device
+            up = lambda t: t.to(dev)
+            if f == "d,s":
+                pos, crd = (up(t) for t in self.index.mode_indices[1])
+            else:
+                crd = up(self.index.mode_indices[1][0])
+                pos = K.coo_rows_to_csr_pos(up(self.index.mode_indices[0][0]), rows)
+            tpos, tcrd, tval = K.csr_transpose(pos, crd, up(self.values), cols)
+            back = (lambda t: t.cpu()) if on_host else (lambda t: t)
+            if f == "d,s":
+                mode_indices = [[], [back(tpos), back(tcrd)]]
+            else:
+                mode_indices = [[back(K.csr_pos_to_coo_rows(tpos, tcrd.numel()))], [back(tcrd)]]
+            values = back(tval)
+        else:
+            raise NotImplementedError(f"change_mode_order for format {f!r}")
+        self.storage = TensorStorage(TensorIndex(mode_indices, self.format, list(mode_order)), values)
+        self.shape = (cols, rows)
+        return self
+
     # -- constructors -----------------------------------------------------------------------------
     @staticmethod
     def from_csr(csr_matrix: torch.Tensor, name: Optional[str] = None) -> "STensor":

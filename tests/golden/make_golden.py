@@ -1,7 +1,8 @@
 """Generate the golden vectors in this directory by running the REFERENCE itself.
 
-Run in a container that has the reference checkout (its location: SCORCH_REFERENCE_ROOT, see the
-default below) and the compiled reference extension (``python oracle/build_ref.py``):
+Run in a container that has the reference checkout (its location: SCORCH_REFERENCE_ROOT, or a
+directory named ``reference`` beside this repository) and the compiled reference extension
+(``python oracle/build_ref.py``):
 
     python tests/golden/make_golden.py
 
@@ -20,10 +21,10 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("SCORCH_REFERENCE_ROOT", "/root/reference")
-
 sys.path.insert(0, ROOT)
-from oracle import ref_loader  # noqa: E402
+from oracle import build_ref, ref_loader  # noqa: E402
+
+REF = build_ref.reference_root()
 
 ref_ops = ref_loader.load()
 assert ref_ops is not None, "build oracle/_ref first (python oracle/build_ref.py)"

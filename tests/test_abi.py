@@ -60,6 +60,15 @@ def test_argument_validation_returns_codes_without_launching(sb_lib):
     # nnz beyond int32: the reference would wrap (csrc/kernels.h:520); here it is an error code
     rc = sb_lib.sb_sddmm_coo_f32(4, 4, 4, 1 << 31, one, one, None, one, 4, one, 4, one, 1, 0, 0, 0, None)
     assert rc == 3
+    # entry counts within a tile of 2^31: the kernels' int tile bounds would overflow
+    rc = sb_lib.sb_spmv_csr_f32(4, 4, (1 << 31) - 100, one, one, one, one, one, one, 1 << 40, None)
+    assert rc == 3 and b"int32" in sb_lib.sb_last_error()
+    rc = sb_lib.sb_sddmm_csr_f32(4, 4, 4, (1 << 31) - 100, one, one, None, one, 4, one, 4, one, None, None,
+                                 1, 0, 0, 0, None)
+    assert rc == 3
+    # the scalar SpMM path (here: float64) has a column limit from the launch grid
+    rc = sb_lib.sb_spmm_csr_typed(1, 4, 4, 65536 * 32, 4, one, one, one, one, 65536 * 32, one, 65536 * 32, None)
+    assert rc == 5 and b"scalar path" in sb_lib.sb_last_error()
     rc = sb_lib.sb_spmv_csr_typed(9, 4, 4, 0, one, one, one, one, one, None)
     assert rc == 5 or rc == 1
     rc = sb_lib.sb_csr_plan_build(4, 4, one, one, 8, None)

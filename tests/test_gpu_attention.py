@@ -123,6 +123,31 @@ def test_sparse_attention_stages_equal_whole_call():
     assert torch.equal(whole, again)      # deterministic
 
 
+def test_mask_values_rewritten_through_the_library_are_seen(oracle):
+    """A mask-values tensor first seen as all ones, then overwritten in place by a library call
+    (out= of another kernel writes through the raw pointer): the attention call must use the
+    new values, not the remembered all-ones verdict."""
+    from scorch_b200 import kernels as K
+    dense, pos, crd, val = make_mask(256, 256, 24, 0.02, seed=11)
+    rng = np.random.default_rng(12)
+    Q, Km, V = (rng.standard_normal((256, 64)).astype(np.float32) * 0.3 for _ in range(3))
+    dpos, dcrd = dev(pos), dev(crd)
+    mv = torch.ones(len(crd), dtype=torch.float32, device="cuda")
+    first = K.sparse_attention_csr(dpos, dcrd, mv, dev(Q), dev(Km), dev(V))
+    ones = np.ones(len(crd), np.float32)
+    ok, err, bad = oracle.allclose_report(first.cpu().numpy(),
+                                          oracle_attention(oracle, pos, crd, ones, Q, Km, V, 1.0), RTOL, ATOL)
+    assert ok, (err, bad)
+    # new mask values = a scaled row softmax of some scores, written into the same tensor
+    K.csr_row_softmax(dpos, dev(val), scale=0.5, out=mv)
+    newval = mv.cpu().numpy()
+    assert not np.allclose(newval, 1.0)
+    second = K.sparse_attention_csr(dpos, dcrd, mv, dev(Q), dev(Km), dev(V))
+    ok, err, bad = oracle.allclose_report(second.cpu().numpy(),
+                                          oracle_attention(oracle, pos, crd, newval, Q, Km, V, 1.0), RTOL, ATOL)
+    assert ok, (err, bad)
+
+
 def test_pipeline_picks_the_attention_call_and_matches_three_operators(oracle):
     from scorch_b200 import pipelines as P, workloads as W
     mask = W.attention_mask(1024, window=64, density=0.01, seed=0)
