@@ -406,9 +406,56 @@ class SpmmWorkload(Workload):
 
     def extras(self, stage_ms):
         ms = stage_ms["spmm_rows_kernel"]
-        return {"gather_model": {"bytes": self.nnz * (8 + self.k * 4) + self.m * self.k * 4,
-                                 "GBps": (self.nnz * (8 + self.k * 4) + self.m * self.k * 4) / (ms * 1e-3) / 1e9,
-                                 "what": "every stored entry counted as one operand-row read"}}
+        gm_bytes = self.nnz * (8 + self.k * 4) + self.m * self.k * 4
+        out = {"gather_model": {"bytes": gm_bytes, "GBps": gm_bytes / (ms * 1e-3) / 1e9,
+                                "what": "every stored entry counted as one operand-row read"}}
+        if self.which == "c3":
+            out["l2_gather"] = self.l2_gather_bound(ms)
+        return out
+
+    def l2_gather_bound(self, ms_default):
+        """What bounds the wide product once DRAM traffic is the compulsory one: the rate at which
+        the L2 hands 1 KB operand-row slices to the SMs.  Measured here with the library's probe
+        kernel (random 1 KB rows of an L2-resident 32 MB panel, nothing else on the critical path)
+        and compared with the product's own L2 -> SM volume (nnz * k * 4 bytes) per second, for the
+        gather kernel and for the bulk-copy (cp.async.bulk through shared memory) kernel."""
+        from scorch_b200 import _lib
+        L = _lib.lib()
+        st = torch.cuda.current_stream().cuda_stream
+
+        def timed(fn, reps=5):
+            fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            b.synchronize()
+            return a.elapsed_time(b) / reps
+
+        rows, warps, gathers = 32768, 148 * 64, 512
+        panel = self.B[:, :256].contiguous()[:rows]
+        sink = torch.zeros(warps, device="cuda", dtype=torch.float32)
+        probe_ms = timed(lambda: _lib.check(L.sb_probe_l2_gather(panel.data_ptr(), panel.shape[0], gathers,
+                                                                 warps, sink.data_ptr(), st)))
+        peak = warps * gathers * 1024 / (probe_ms * 1e-3) / 1e9
+        volume = self.nnz * self.k * 4
+        per_kernel = {}
+        before = L.sb_spmm_wide_select(-1)
+        try:
+            for name, mode in (("gather kernel (ld.global.nc.v8 through L1)", 0),
+                               ("bulk-copy kernel (cp.async.bulk through shared memory)", 1)):
+                L.sb_spmm_wide_select(mode)
+                t = timed(lambda: self.K.spmm_csr(self.pos, self.crd, self.val, self.B, plan=self.plan,
+                                                  out=self.out), reps=10)
+                per_kernel[name] = {"ms": t, "l2_to_sm_GBps": volume / (t * 1e-3) / 1e9,
+                                    "frac_of_probe": volume / (t * 1e-3) / 1e9 / peak}
+        finally:
+            L.sb_spmm_wide_select(before)
+        return {"probe_GBps": peak, "probe": f"{warps} warps x {gathers} random 1 KB rows of a "
+                f"{panel.shape[0]} x 256 fp32 panel (L2 resident)", "l2_to_sm_bytes_per_launch": volume,
+                "kernels": per_kernel, "selected": "bulk-copy" if before == 1 else "gather",
+                "wide_status": L.sb_spmm_wide_status()}
 
     def e2e_step(self):
         for dst, src in zip(self.stage, self.host):

@@ -116,6 +116,24 @@ SB_API int sb_spmm_csr_acc_f32(int64_t m, int64_t n, int64_t k, int64_t nnz, con
                                const void* plan, int64_t plan_segments, void* scratch,
                                size_t scratch_bytes, void* stream);
 
+/* Wide dense operands (k >= 512, one matrix, no heavy rows) have a second kernel: operand rows
+ * staged through shared memory by 1-D bulk copies (cp.async.bulk + mbarrier) instead of gathers
+ * through L1 and registers.  sb_spmm_wide_select(1 | 0) picks the bulk-copy / the gather kernel
+ * for later sb_spmm_csr_f32 calls of this process and returns the previous choice (any other
+ * argument only queries); the first choice comes from the environment variable
+ * SCORCH_B200_SPMM_WIDE = "tma" | "gather", else it is the one measured faster on B200.  All waits
+ * in that kernel are bounded; sb_spmm_wide_status() (synchronises) returns 0, or 1 / 2 when a
+ * producer / consumer wait ever gave up, or -1 when the status could not be read.
+ * sb_probe_l2_gather launches a measurement kernel: `warps` warps (multiple of 8) each read
+ * `gathers_per_warp` (multiple of 4) pseudo-random 1 KB rows of the `rows` x 256 fp32 `panel`
+ * (rows < 2^24) — the load pattern of such a product with nothing else on the critical path;
+ * timed by the caller, it gives the L2 gather rate a wide SpMM can at best reach.  `out`: one
+ * float per warp.  No reference counterpart (measurement aid). */
+SB_API int sb_spmm_wide_select(int mode);
+SB_API int sb_spmm_wide_status(void);
+SB_API int sb_probe_l2_gather(const float* panel, int64_t rows, int64_t gathers_per_warp, int64_t warps,
+                              float* out, void* stream);
+
 /* Same product for the other registry dtypes (SB_F64, SB_I32, SB_I64; SB_F32 also accepted).
  * Integer products wrap like the reference's C++ arithmetic.
  * Replaces: prebuilt_spmm_csr_{f64,i32,i64}, spmm_csr_double (csrc/ops.cpp:91-116). */

@@ -34,6 +34,9 @@ SIGNATURES = {
                                _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _sz, _ptr]),
     "sb_spmm_csr_acc_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _int,
                                    _ptr, _i64, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _sz, _ptr]),
+    "sb_spmm_wide_select": (_int, [_int]),
+    "sb_spmm_wide_status": (_int, []),
+    "sb_probe_l2_gather": (_int, [_ptr, _i64, _i64, _i64, _ptr, _ptr]),
     "sb_spmm_csr_typed": (_int, [_int, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                  _i64, _ptr]),
     "sb_spmv_csr_scratch_bytes": (_sz, [_i64]),

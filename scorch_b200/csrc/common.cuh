@@ -80,6 +80,12 @@ int spmm_remainder(int64_t m, int64_t k, const int* rem_pos, const int* rem_ent,
                    float* C, int64_t ldc, int64_t batch, int64_t stride_val, int64_t stride_b,
                    int64_t stride_c, int val_compact, cudaStream_t st);
 
+// SpMM over wide dense operands with the operand rows staged through shared memory by bulk
+// copies (spmm_wide.cu); `spmm_wide_wanted` tells whether that kernel is selected.
+bool spmm_wide_wanted();
+int spmm_wide_launch(int64_t m, int64_t k, const int* pos, const int* crd, const float* val, const float* B,
+                     int64_t ldb, const float* bias, int relu, float* C, int64_t ldc, cudaStream_t st);
+
 // ---- device helpers ------------------------------------------------------------------------
 #ifdef __CUDACC__
 

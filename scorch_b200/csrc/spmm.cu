@@ -759,6 +759,9 @@ static int spmm_csr_f32_impl(int64_t m, int64_t n, int64_t k, int64_t nnz, const
         return fail(SB_ERR_WORKSPACE, "spmm: scratch has %zu bytes, needs %zu", scratch_bytes, need);
     }
   }
+  // wide operands, no heavy rows: optionally the bulk-copy kernel of spmm_wide.cu
+  if (k >= 512 && batch == 1 && !accumulate && !(plan && plan_segments != 0) && spmm_wide_wanted())
+    return spmm_wide_launch(m, k, pos, crd, val, B, ldb, bias, relu, C, ldc, st);
   SpmmArgs a;
   a.m = (int)m; a.k = (int)k; a.pos = pos; a.crd = crd; a.val = val; a.B = B; a.ldb = ldb;
   a.bias = bias; a.relu = relu; a.C = C; a.ldc = ldc;
