@@ -193,10 +193,12 @@ class SparseAttention(Workload):
     """Config 2: SDDMM + row softmax + SpMM, (batch*heads) independent units sharing one mask."""
     name = "c2_sparse_attention_seq4096_h8_d64_b4_band128_rand1pct"
 
-    def __init__(self, batch=4, heads=8, seq=4096, d=64, window=128, density=0.01):
+    def __init__(self, batch=4, heads=8, seq=4096, d=64, window=128, density=0.01, world=1):
         self.batch, self.heads, self.seq, self.d = batch, heads, seq, d
         self.window, self.density = window, density
-        self.units = batch * heads
+        self.units_total = batch * heads
+        self.units = self.units_total     # this rank's share once set up
+        self.world = world
 
     def host_inputs(self, units=None, rank=0):
         from scorch_b200 import workloads as W
@@ -207,9 +209,13 @@ class SparseAttention(Workload):
         return W.attention_qkv(1, units, self.seq, self.d, seed=1 + rank)
 
     def setup(self, rank: int):
-        from scorch_b200 import kernels as K, pipelines as P
+        from scorch_b200 import kernels as K, pipelines as P, sharded as S
         self.K = K
-        Q, Km, V = self.host_inputs(rank=rank)
+        Q, Km, V = self.host_inputs(rank=0)
+        # the (batch, head) units are independent: each rank takes a contiguous share of them
+        u0, u1 = S.unit_range(self.units_total, rank, self.world)
+        self.units = u1 - u0
+        Q, Km, V = (t[u0:u1].contiguous() for t in (Q, Km, V))
         self.host = [t.pin_memory() for t in (Q, Km, V)]
         self.host_out = torch.empty((self.units, self.seq, self.d), dtype=torch.float32).pin_memory()
         self.pos, self.crd, self.mval = (t.cuda() for t in (self.mask.pos, self.mask.crd, self.mask.val))
@@ -231,16 +237,19 @@ class SparseAttention(Workload):
         self.host_api = P.HostSparseAttention(self.pos, self.crd, self.mval, self.units, self.seq, self.d)
 
     @property
-    def flops_per_step(self):  # SDDMM + SpMM, 2*nnz*d each (the reference tools' convention)
-        return 2 * (2.0 * self.nnz * self.d) * self.units
+    def flops_total(self):  # SDDMM + SpMM, 2*nnz*d each (the reference tools' convention)
+        return 2 * (2.0 * self.nnz * self.d) * self.units_total
 
     def config(self):
-        return {"workload": self.name, "units_per_gpu": self.units, "seq": self.seq, "head_dim": self.d,
-                "mask_nnz": self.nnz, "l2": "inputs larger than L2"}
+        return {"workload": self.name, "units": self.units_total, "seq": self.seq, "head_dim": self.d,
+                "mask_nnz": self.nnz,
+                "parallelism": f"(batch, head) units split over {self.world} GPU(s), no communication",
+                "l2": "inputs larger than L2"}
 
     def run_info(self):
         bp = self.attn_plan or self.block_plan
-        return {"path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
+        return {"units_this_rank": self.units,
+                "path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
                          if self.attn_plan else "sddmm, row softmax, spmm"),
                 "blocks_16x16": bp.blocks if bp else 0,
                 "entries_outside_blocks": bp.rem_nnz if bp else self.nnz}
@@ -345,15 +354,16 @@ class SparseAttention(Workload):
         dt = (time.perf_counter() - t0) / repeats
         flops = 2 * (2.0 * nnz * d) * units
         kind = "reference" if ref is not None else "port"
-        return flops / dt / 1e9, kind, dt, (f"{units} of {self.units} heads per step: sddmm_coo_float_prebuilt + "
+        return flops / dt / 1e9, kind, dt, (f"{units} of {self.units_total} heads per step: sddmm_coo_float_prebuilt + "
                                             f"row softmax + spmm_csr_float_v2 ({kind})")
 
 
 class SpmmWorkload(Workload):
     """Configs 1 and 3: one CSR x dense product."""
 
-    def __init__(self, which: str):
+    def __init__(self, which: str, world: int = 1):
         self.which = which
+        self.world = world
         self.name = {"c1": "c1_spmm_4096x4096_1pct_k64", "c3": "c3_sae_decode_8192x32768_top32_k4096"}[which]
 
     def setup(self, rank: int):
@@ -367,10 +377,18 @@ class SpmmWorkload(Workload):
             A = W.sae_activations(8192, 32768, 32, seed=0, device=dev).to("cpu")
             B = W.sae_decoder(32768, 4096, seed=1, device=dev).cpu()
         self.A = A
-        self.m, self.n, self.k, self.nnz = A.shape[0], A.shape[1], B.shape[1], A.nnz
+        self.m_total, self.nnz_total = A.shape[0], A.nnz
+        self.n, self.k = A.shape[1], B.shape[1]
+        self.m, self.nnz = self.m_total, self.nnz_total
         self.host = [A.val, B]
         if dev == "cpu":
             return
+        if self.world > 1:
+            # rows of A balanced by stored entries, the dense operand held by every rank
+            from scorch_b200 import sharded as S
+            blk, self.bounds = S.row_block(A.pos, A.crd, A.val, rank, self.world)
+            A = W.Csr((blk.rows, self.n), blk.pos, blk.crd, blk.val)
+            self.m, self.nnz = blk.rows, blk.nnz
         self.host = [A.val.pin_memory(), B.pin_memory()]
         self.pos, self.crd = A.pos.cuda(), A.crd.cuda()
         self.val, self.B = (t.cuda() for t in self.host)
@@ -382,13 +400,17 @@ class SpmmWorkload(Workload):
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if self.which == "c1" else None
 
     @property
-    def flops_per_step(self):
-        return 2.0 * self.nnz * self.k
+    def flops_total(self):
+        return 2.0 * self.nnz_total * self.k
 
     def config(self):
-        return {"workload": self.name, "m": self.m, "n": self.n, "k": self.k, "nnz": self.nnz,
+        return {"workload": self.name, "m": self.m_total, "n": self.n, "k": self.k, "nnz": self.nnz_total,
+                "parallelism": f"rows split by stored entries over {self.world} GPU(s), dense operand replicated",
                 "l2": "L2 flushed by a 256 MiB write between iterations" if self.which == "c1"
                 else "inputs larger than L2"}
+
+    def run_info(self):
+        return {"rows_this_rank": self.m, "nnz_this_rank": self.nnz}
 
     def alg_bytes(self):
         return {"spmm_rows_kernel": (self.m + 1) * 4 + self.nnz * 8 + self.n * self.k * 4 + self.m * self.k * 4}
@@ -482,7 +504,7 @@ class SpmmWorkload(Workload):
 
         def one():
             if ref is not None:
-                ref.spmm_csr_float_v2([self.m, self.k], [self.m, self.n], [[], [A.pos, A.crd]], A.val,
+                ref.spmm_csr_float_v2([self.m_total, self.k], [self.m_total, self.n], [[], [A.pos, A.crd]], A.val,
                                       [self.n, self.k], [[], []], B.reshape(-1), 256)
             else:
                 O.spmm_csr_v2(A.pos.numpy(), A.crd.numpy(), A.val.numpy(), B.numpy())
@@ -492,7 +514,7 @@ class SpmmWorkload(Workload):
             one()
         dt = (time.perf_counter() - t0) / repeats
         kind = "reference" if ref is not None else "port"
-        return self.flops_per_step / dt / 1e9, kind, dt, f"the whole product, spmm_csr_float_v2 ({kind})"
+        return self.flops_total / dt / 1e9, kind, dt, f"the whole product, spmm_csr_float_v2 ({kind})"
 
 
 class SpgemmSpmv(Workload):
@@ -501,38 +523,49 @@ class SpgemmSpmv(Workload):
     name = "c5_spmspm_spmv_2M_powerlaw"
     SPMV_SWEEP = 10  # back-to-back SpMV calls per step: keeps the GPU busy between launches
 
-    def __init__(self, n=2_000_000):
-        self.n = n
+    def __init__(self, n=2_000_000, world=1):
+        self.n, self.world = n, world
 
     def setup(self, rank: int):
-        from scorch_b200 import kernels as K, workloads as W
-        self.K = K
+        from scorch_b200 import kernels as K, sharded as S, workloads as W
+        self.K, self.S = K, S
         A = W.powerlaw_square(self.n, seed=0, device="cuda")
         self.A = A
         self.nnz = A.nnz
         self.x = W.randn_on((self.n,), seed=1, device="cuda")
-        self.plan = K.CsrPlan(A.pos, self.nnz)
         lens = (A.pos[1:] - A.pos[:-1]).long()
         self.products = int(lens[A.crd.long()].sum().item())
+        # SpMV: rows balanced by stored entries; SpGEMM: rows of A balanced by products; the other
+        # operand (x / the whole A) is held by every rank
+        self.mv, _ = S.row_block(A.pos, A.crd, A.val, rank, self.world)
+        self.mm, _ = S.row_block(A.pos, A.crd, A.val, rank, self.world,
+                                 bounds=S.product_bounds(A.pos, A.crd, A.pos, self.world))
         self.timings = []
 
     @property
-    def flops_per_step(self):
+    def flops_total(self):
         return 2.0 * self.products + 2.0 * self.nnz * self.SPMV_SWEEP
 
     def config(self):
         return {"workload": self.name, "n": self.n, "nnz": self.nnz, "products": self.products,
-                "spmv_calls_per_step": self.SPMV_SWEEP, "l2": "inputs larger than L2"}
+                "spmv_calls_per_step": self.SPMV_SWEEP,
+                "parallelism": f"SpMV rows split by stored entries, SpGEMM rows by products, over "
+                               f"{self.world} GPU(s); x and the right operand replicated",
+                "l2": "inputs larger than L2"}
 
     def run_info(self):
-        return {"nnz_C": getattr(self, "nnzc", None)}
+        return {"nnz_C_this_rank": getattr(self, "nnzc", None), "spmv_rows_this_rank": self.mv.rows,
+                "spgemm_rows_this_rank": self.mm.rows}
 
     def alg_bytes(self):
         n, nnz = self.n, self.nnz
         nnzc = getattr(self, "nnzc", 0)
-        return {"spmv": (n + 1) * 4 + nnz * 8 + 2 * n * 4,
-                "spgemm_symbolic": (n + 1) * 4 + nnz * 4 + (n + 1) * 4,
-                "spgemm_numeric": (n + 1) * 4 + nnz * 8 + (n + 1) * 4 + nnzc * 8}
+        mv, mm = self.mv, self.mm
+        # per rank: its rows of the left operand, the replicated operand read once, its outputs
+        return {"spmv": (mv.rows + 1) * 4 + mv.nnz * 8 + n * 4 + mv.rows * 4,
+                "spgemm_symbolic": (mm.rows + 1) * 4 + mm.nnz * 4 + (n + 1) * 4 + nnz * 4 + (mm.rows + 1) * 4,
+                "spgemm_numeric": (mm.rows + 1) * 4 + mm.nnz * 8 + (n + 1) * 4 + nnz * 8 + (mm.rows + 1) * 4
+                                  + nnzc * 8}
 
     kernels = ("spmv", "spgemm_symbolic", "spgemm_numeric")
     launches_per_step = 12
@@ -541,15 +574,15 @@ class SpgemmSpmv(Workload):
         self.timings = []
 
     def step(self, ev=None):
-        A = self.A
+        A, mv, mm = self.A, self.mv, self.mm
         if ev is not None:
             ev[0].record()
         for _ in range(self.SPMV_SWEEP):
-            self.y = self.K.spmv_csr(A.pos, A.crd, A.val, self.x, plan=self.plan)
+            self.y = self.K.spmv_csr(mv.pos, mv.crd, mv.val, self.x)
         if ev is not None:
             ev[1].record()
         t = {}
-        cpos, ccrd, cval = self.K.spgemm_csr(A.pos, A.crd, A.val, A.pos, A.crd, A.val, self.n, timings=t)
+        cpos, ccrd, cval = self.K.spgemm_csr(mm.pos, mm.crd, mm.val, A.pos, A.crd, A.val, self.n, timings=t)
         self.nnzc = int(ccrd.numel())
         if ev is not None:
             self.timings.append(t)
@@ -642,8 +675,8 @@ class GcnSharded(Workload):
         self.timeline = None
 
     @property
-    def flops_per_step(self):  # the two sparse products (2*nnz*k); per-rank share is 1/world
-        return 2.0 * self.nnz_global * (self.K1 + self.K2) / self.world
+    def flops_total(self):  # the two sparse products (2*nnz*k) of the whole graph
+        return 2.0 * self.nnz_global * (self.K1 + self.K2)
 
     def config(self):
         return {"workload": self.name, "nodes": self.n, "nnz": self.nnz_global, "max_row_nnz": self.max_row,
@@ -655,10 +688,11 @@ class GcnSharded(Workload):
                 "l2": "inputs larger than L2"}
 
     def run_info(self):
-        segs = [b.plan.segments if b.plan is not None else None for b in self.shard.blocks]
+        sp = self.shard.splits
+        segs = [b.plan.segments if b.plan is not None else None for b in sp[0].blocks]
         return {"rows_this_rank": self.shard.rows, "nnz_this_rank": self.shard.nnz,
-                "row_chunks_per_layer": self.shard.chunks, "chunk_rows": self.shard.chunk_rows,
-                "heavy_segments_per_chunk": segs}
+                "row_chunk_offsets_layer1": sp[0].offsets, "row_chunk_offsets_layer2": sp[-1].offsets,
+                "heavy_segments_per_chunk_layer1": segs}
 
     def alg_bytes(self):
         rows, nnz, n = self.shard.rows, self.shard.nnz, self.n
@@ -670,7 +704,7 @@ class GcnSharded(Workload):
     @property
     def launches_per_step(self):
         # per layer one SpMM launch per row chunk (rows and heavy-row segments share the launch)
-        return 2 * self.shard.chunks
+        return self.shard.splits[0].chunks + self.shard.splits[-1].chunks
 
     def begin_block(self):
         self.timeline = self.S.Timeline()
@@ -805,11 +839,11 @@ def make_workload(name: str, world: int = 1, c4_nodes: int = 2_000_000):
     if name == "c4":
         return GcnSharded(n=c4_nodes, world=world)
     if name == "c2":
-        return SparseAttention()
+        return SparseAttention(world=world)
     if name in ("c1", "c3"):
-        return SpmmWorkload(name)
+        return SpmmWorkload(name, world=world)
     if name == "c5":
-        return SpgemmSpmv()
+        return SpgemmSpmv(world=world)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -858,7 +892,7 @@ def measure_e2e(wl, K: int, world: int, barrier, max_over_ranks):
     b.record()
     barrier()
     ms = max_over_ranks(a.elapsed_time(b)) / K
-    return {"value": wl.flops_per_step * world / (ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms,
+    return {"value": wl.flops_total / (ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms,
             "steps": K, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes}
 
 
@@ -913,7 +947,7 @@ def run_reference(args, rank: int, emit):
     threads = host_threads()
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.median(dts) * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.workload == "c4" else "weak",
+            "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads["openmp_threads"], "kind": kind,
                              "sample": sample, "threads": threads},
@@ -1006,8 +1040,8 @@ def main():
         sampler.start()
     step_ms, stage_ms, nblocks, block_ms = measure(wl, K, W_, world, barrier, max_over_ranks,
                                                    args.min_seconds, 50)
-    value = wl.flops_per_step * world / (step_ms * 1e-3) / 1e9
-    scaling = "strong" if args.workload == "c4" else "weak"
+    value = wl.flops_total / (step_ms * 1e-3) / 1e9
+    scaling = "strong"   # every workload is a fixed problem that the ranks share
     e2e = measure_e2e(wl, min(K, 10) if args.workload == "c4" else K, world, barrier, max_over_ranks)
     clocks = sampler.stop() if rank == 0 else None
 
@@ -1042,7 +1076,7 @@ def main():
             k2 = K if name != "c5" else min(K, 3)
             ms, st, nb, _ = measure(w2, k2, 3, 1, barrier, max_over_ranks, 0.3, 20)
             entry = {"config": w2.config(), "run": w2.run_info(), "ms_per_step": ms, "steps": k2, "blocks": nb,
-                     "value": w2.flops_per_step / (ms * 1e-3) / 1e9, "unit": UNIT,
+                     "value": w2.flops_total / (ms * 1e-3) / 1e9, "unit": UNIT,
                      "roofline": roofline_of(w2, st), **w2.extras(st),
                      "e2e": measure_e2e(w2, min(k2, 10), 1, barrier, max_over_ranks)}
             if not args.no_cpu_baseline:

@@ -309,6 +309,27 @@ SB_API int sb_spgemm_numeric(int dtype, int64_t m, int64_t kb, int64_t n, const 
                              int32_t* Ccrd, void* Cval, void* ws, size_t ws_bytes, void* stream);
 
 /* --------------------------------------------------------------------------------------------
+ * Element-wise product / sum of two CSR matrices of the same shape, CSR out with ascending columns:
+ *   SB_EWISE_MUL  C = A .* B, stored where both operands store an entry;
+ *   SB_EWISE_ADD  C = A + B,  stored where either operand stores an entry.
+ * The structure is symbolic (a result that happens to be zero stays stored).  Two calls, like
+ * SpGEMM: _symbolic writes Cpos[0..m] and returns the number of stored entries (synchronises), the
+ * caller allocates Ccrd / Cval, _numeric fills them.  `ws`: sb_csr_ewise_workspace_bytes(m) bytes.
+ * Replaces: the loops the reference's compiler emits for einsum("ij,ij->ij", A, B) and A + B over
+ *           compressed operands (src/scorch/ops.py:375-819; covered by
+ *           tests/test_scorch/test_kernels_comprehensive.py:119-200).
+ * -------------------------------------------------------------------------------------------- */
+enum { SB_EWISE_MUL = 0, SB_EWISE_ADD = 1 };
+SB_API size_t sb_csr_ewise_workspace_bytes(int64_t m);
+SB_API int sb_csr_ewise_symbolic(int op, int64_t m, const int32_t* Apos, const int32_t* Acrd,
+                                 const int32_t* Bpos, const int32_t* Bcrd, int32_t* Cpos,
+                                 int64_t* nnz_host, void* ws, size_t ws_bytes, void* stream);
+SB_API int sb_csr_ewise_numeric(int op, int dtype, int64_t m, const int32_t* Apos, const int32_t* Acrd,
+                                const void* Aval, const int32_t* Bpos, const int32_t* Bcrd,
+                                const void* Bval, const int32_t* Cpos, int32_t* Ccrd, void* Cval,
+                                void* stream);
+
+/* --------------------------------------------------------------------------------------------
  * Format plumbing on the device (the reference does these with torch ops before dispatch,
  * src/scorch/stensor.py:785-896): sorted COO rows -> CSR row pointers, CSR row pointers -> row
  * ids.

@@ -255,3 +255,27 @@ def topk_rows_to_csr(X, k, relu=False):
         val[i] = np.maximum(X[i, pick], 0) if relu else X[i, pick]
     pos = (np.arange(m + 1) * k).astype(np.int32)
     return pos, crd.reshape(-1), val.reshape(-1)
+
+
+def csr_ewise(op, Apos, Acrd, Aval, Bpos, Bcrd, Bval):
+    """Element-wise "mul" / "add" of two CSR matrices with the reference's output structure: the
+    intersection / union of the stored columns per row, ascending, zeros that arise kept (what
+    the compiler-emitted merge loops of the reference produce; pinned by the golden cases
+    ewise_f32)."""
+    Apos, Acrd, Bpos, Bcrd = (np.asarray(x) for x in (Apos, Acrd, Bpos, Bcrd))
+    Aval, Bval = np.asarray(Aval), np.asarray(Bval)
+    m = len(Apos) - 1
+    pos, crd, val = [0], [], []
+    for i in range(m):
+        a = {int(c): Aval[p] for p, c in zip(range(Apos[i], Apos[i + 1]), Acrd[Apos[i]:Apos[i + 1]])}
+        b = {int(c): Bval[p] for p, c in zip(range(Bpos[i], Bpos[i + 1]), Bcrd[Bpos[i]:Bpos[i + 1]])}
+        cols = sorted(set(a) & set(b)) if op == "mul" else sorted(set(a) | set(b))
+        for c in cols:
+            crd.append(c)
+            if op == "mul":
+                val.append(a[c] * b[c])
+            else:
+                val.append(a[c] + b[c] if c in a and c in b else (a[c] if c in a else b[c]))
+        pos.append(len(crd))
+    return (np.asarray(pos, np.int32), np.asarray(crd, np.int32),
+            np.asarray(val, Aval.dtype) if val else np.zeros(0, Aval.dtype))

@@ -10,11 +10,11 @@ Like the reference (src/scorch/__init__.py:14-18) unknown attributes fall throug
 from __future__ import annotations
 
 from .stensor import STensor, TensorFormat, TensorIndex, TensorStorage, parse_format
-from .ops import einsum, matmul, spmm_bias_act
+from .ops import add, einsum, elementwise, matmul, spmm_bias_act
 from . import scorch_ops
 
-__all__ = ["STensor", "TensorFormat", "TensorIndex", "TensorStorage", "parse_format", "einsum",
-           "matmul", "spmm_bias_act", "scorch_ops"]
+__all__ = ["STensor", "TensorFormat", "TensorIndex", "TensorStorage", "parse_format", "add", "einsum",
+           "elementwise", "matmul", "spmm_bias_act", "scorch_ops"]
 
 
 def __getattr__(name):

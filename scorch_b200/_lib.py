@@ -68,6 +68,9 @@ SIGNATURES = {
                                   C.POINTER(_i64), _ptr, _sz, _ptr]),
     "sb_spgemm_numeric": (_int, [_int, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
                                  _ptr, _ptr, _ptr, _sz, _ptr]),
+    "sb_csr_ewise_workspace_bytes": (_sz, [_i64]),
+    "sb_csr_ewise_symbolic": (_int, [_int, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, C.POINTER(_i64), _ptr, _sz, _ptr]),
+    "sb_csr_ewise_numeric": (_int, [_int, _int, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "sb_dense_to_csr_workspace_bytes": (_sz, [_i64]),
     "sb_dense_to_csr_count": (_int, [_i64, _i64, _ptr, _i64, _ptr, C.POINTER(_i64), _ptr, _sz, _ptr]),
     "sb_dense_to_csr_fill": (_int, [_i64, _i64, _ptr, _i64, _ptr, _ptr, _ptr, _ptr]),

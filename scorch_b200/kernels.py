@@ -565,3 +565,36 @@ def topk_rows_to_csr(X: torch.Tensor, k: int, relu: bool = False):
         check(_lib.lib().sb_topk_rows_to_csr_f32(m, n, k, X.data_ptr(), X.stride(0), int(bool(relu)),
                                                  pos.data_ptr(), crd.data_ptr(), val.data_ptr(), _stream()))
     return pos, crd, val
+
+
+def csr_ewise(op: str, Apos, Acrd, Aval, Bpos, Bcrd, Bval):
+    """Element-wise ``"mul"`` (stored where both operands store an entry) or ``"add"`` (where
+    either does) of two CSR matrices of the same shape: (Cpos, Ccrd, Cval), columns ascending,
+    symbolic structure kept.  The loops the reference's compiler emits for
+    ``einsum("ij,ij->ij", A, B)`` and ``A + B`` over compressed operands."""
+    code_op = {"mul": 0, "add": 1}[op]
+    Apos, Acrd = _dev(Apos, torch.int32, "Apos"), _dev(Acrd, torch.int32, "Acrd")
+    Bpos, Bcrd = _dev(Bpos, torch.int32, "Bpos"), _dev(Bcrd, torch.int32, "Bcrd")
+    code = _DTYPE_CODE.get(Aval.dtype)
+    if code is None or Bval.dtype != Aval.dtype:
+        raise TypeError("element-wise operands must share one of f32/f64/i32/i64")
+    Aval, Bval = _dev(Aval, Aval.dtype, "Aval"), _dev(Bval, Aval.dtype, "Bval")
+    m = Apos.numel() - 1
+    if Bpos.numel() - 1 != m:
+        raise ValueError("operands differ in row count")
+    L = _lib.lib()
+    dev = Aval.device
+    with torch.cuda.device(dev):
+        wbytes = L.sb_csr_ewise_workspace_bytes(m)
+        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        Cpos = torch.empty(m + 1, dtype=torch.int32, device=dev)
+        total = C.c_int64(0)
+        check(L.sb_csr_ewise_symbolic(code_op, m, Apos.data_ptr(), Acrd.data_ptr(), Bpos.data_ptr(),
+                                      Bcrd.data_ptr(), Cpos.data_ptr(), C.byref(total), ws.data_ptr(), wbytes,
+                                      _stream()))
+        Ccrd = torch.empty(total.value, dtype=torch.int32, device=dev)
+        Cval = torch.empty(total.value, dtype=Aval.dtype, device=dev)
+        check(L.sb_csr_ewise_numeric(code_op, code, m, Apos.data_ptr(), Acrd.data_ptr(), Aval.data_ptr(),
+                                     Bpos.data_ptr(), Bcrd.data_ptr(), Bval.data_ptr(), Cpos.data_ptr(),
+                                     Ccrd.data_ptr(), Cval.data_ptr(), _stream()))
+    return Cpos, Ccrd, Cval

@@ -193,6 +193,8 @@ def einsum(expression: str, *tensors: Union[torch.Tensor, STensor], **kwargs: An
             r = native_ops.sddmm_csr_float(*args)
             return _wrap(r, S.shape, "o,o")
         raise NotImplementedError(f"SDDMM mask format {S.format}")
+    if expr == "ij,ij->ij" and len(ts) == 2:
+        return elementwise("mul", ts[0], ts[1], **kwargs)
     if expr == "ij,jk->ik" and len(ts) == 2:
         return matmul(ts[0], ts[1], **kwargs)
     if expr == "ij,j->i" and len(ts) == 2:
@@ -200,6 +202,57 @@ def einsum(expression: str, *tensors: Union[torch.Tensor, STensor], **kwargs: An
     raise NotImplementedError(
         f"einsum expression {expression!r} is outside the sparse hot path (SpMM, SDDMM, SpMV, "
         "SpGEMM); the reference would JIT-compile it")
+
+
+def elementwise(op: str, a: Union[torch.Tensor, STensor], b: Union[torch.Tensor, STensor], **kwargs: Any
+                ) -> STensor:
+    """``"mul"``: C[i,j] = A[i,j] * B[i,j];  ``"add"``: C = A + B, for two sparse matrices of the same
+    shape in the same format, compressed (``d,s``) or coordinate (``o,o``); the result has that
+    format, its structure the intersection / union of the operands' (the reference compiles a merge
+    loop for these, src/scorch/ops.py:375-819; tests/test_scorch/test_kernels_comprehensive.py:119-200).
+    Host operands are moved to the GPU for the kernel and the result comes back to the host."""
+    from . import kernels as K
+    a = STensor.from_torch(a) if isinstance(a, torch.Tensor) else a
+    b = STensor.from_torch(b) if isinstance(b, torch.Tensor) else b
+    fa, fb = str(a.format), str(b.format)
+    requested = kwargs.get("format", kwargs.get("output_format"))
+    if a.shape != b.shape or a.dim() != 2:
+        raise ValueError("element-wise operands must be matrices of the same shape")
+    if fa != fb or fa not in ("d,s", "o,o") or a.dtype != b.dtype or (
+            requested is not None and str(parse_format(requested)) != fa):
+        raise NotImplementedError(
+            f"no B200 kernel for element-wise {op} of {fa} and {fb} operands ({a.dtype}/{b.dtype}, output "
+            f"{requested}); the reference would JIT-compile it")
+    for t in (a, b):
+        if t.index.mode_order != [0, 1]:
+            raise NotImplementedError("element-wise operands must be in the default mode order")
+    host = not a.values.is_cuda
+    dev = torch.device("cuda", torch.cuda.current_device()) if host else a.values.device
+    up = lambda t: t.to(dev)
+
+    def csr_of(t):
+        if str(t.format) == "d,s":
+            return up(t.index.mode_indices[1][0]), up(t.index.mode_indices[1][1])
+        return (K.coo_rows_to_csr_pos(up(t.index.mode_indices[0][0]), t.shape[0]),
+                up(t.index.mode_indices[1][0]))
+    (apos, acrd), (bpos, bcrd) = csr_of(a), csr_of(b)
+    start = time.time()
+    cpos, ccrd, cval = K.csr_ewise(op, apos, acrd, up(a.values), bpos, bcrd, up(b.values))
+    time_dict = kwargs.get("time_dict")
+    if time_dict is not None:
+        torch.cuda.current_stream().synchronize()
+        time_dict["eval_time"] = time.time() - start
+    back = (lambda t: t.cpu()) if host else (lambda t: t)
+    if fa == "d,s":
+        idx = TensorIndex([[], [back(cpos), back(ccrd)]], "d,s")
+    else:
+        idx = TensorIndex([[back(K.csr_pos_to_coo_rows(cpos, ccrd.numel()))], [back(ccrd)]], "o,o")
+    return STensor(shape=a.shape, index=idx, value=back(cval))
+
+
+def add(a: Union[torch.Tensor, STensor], b: Union[torch.Tensor, STensor], **kwargs: Any) -> STensor:
+    """A + B for two sparse matrices (what ``STensor.__add__`` of the reference computes)."""
+    return elementwise("add", a, b, **kwargs)
 
 
 def spmm_bias_act(a: Union[torch.Tensor, STensor], b: torch.Tensor, bias: torch.Tensor,

@@ -10,9 +10,11 @@ csrc/spmm.h:2035-2077); this module is the multi-GPU form of the same products:
   (``sharded_spmm_replicated``);
 * the dense operand of a GCN layer is produced row-sharded by the previous layer, so every
   layer all-gathers it (NCCL over NVLink).  The gather is cut into ROW CHUNKS: every rank's
-  block of operand rows is cut into ``chunks`` equal pieces, gather c collects piece c of every
-  rank, and the rank's matrix block is split once, at set-up, into ``chunks`` sub-matrices, the
-  c-th holding the entries whose column falls into piece c of its owner.  The layer is then
+  block of operand rows is cut into pieces at the same offsets (equal pieces, or in given
+  proportions: a small first piece shortens the start-up during which nothing can be
+  multiplied yet), gather c collects piece c of every rank, and the rank's matrix block is
+  split once, at set-up, into sub-matrices, the c-th holding the entries whose column falls
+  into piece c of its owner.  The layer is then
 
       C  = A_0 G_0;   C += A_1 G_1;   ...;   C = act(C + A_last G_last)
 
@@ -20,11 +22,20 @@ csrc/spmm.h:2035-2077); this module is the multi-GPU form of the same products:
   pass reads full-width operand rows (1 KB at 256 columns) and reads its part of the matrix
   once; the random gathers of one pass are confined to one chunk of the operand, which the L2
   cache holds a good part of;
-* blocks have different row counts, so each rank's block is padded to ``chunks * chunk_rows``
-  rows and the column indices are remapped ONCE, at set-up, to the gathered layout of their
-  chunk (column j, owned by rank q at offset o, chunk c = o // chunk_rows, becomes
-  q * chunk_rows + o - c * chunk_rows).  Nothing is repacked at run time and gathered data
-  always lands in local HBM before a kernel reads it.
+* SpMV shards like SpMM with a replicated operand (``sharded_spmv``; ``gather_vector`` when every
+  rank needs the whole result); SpGEMM shards by row blocks of A balanced by the number of
+  products (``product_bounds``), B replicated, each rank running both phases on its block; one
+  all-gather of the per-rank entry counts turns the local row pointers into global ones
+  (``sharded_spgemm``);
+* the (batch, head) units of a sparse-attention call are independent: ``unit_range`` gives each
+  rank a contiguous share, no communication;
+* blocks have different row counts, so each rank's block is padded to the largest block and the
+  column indices are remapped ONCE, at set-up, to the gathered layout of their chunk (column j,
+  owned by rank q at offset o inside chunk c = [start_c, start_c + rows_c), becomes
+  q * rows_c + o - start_c).  Nothing is repacked at run time and gathered data always lands in
+  local HBM before a kernel reads it;
+* the two layers of a GCN may be cut differently (``chunks=(first, second)``): the wide first
+  layer into a few large pieces, the narrow second one into more.
 
 ``spmm_fn`` lets the CPU tests (gloo) run this host logic with a CPU SpMM; the default is the
 CUDA kernel.
@@ -79,34 +90,69 @@ def row_block(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, rank: int
     return CsrBlock(lpos, crd[p0:p1].contiguous(), val[p0:p1].contiguous()), bounds
 
 
-def default_chunks(world: int) -> int:
-    """Row chunks per layer: none with one rank (nothing to overlap), eight otherwise."""
+def default_chunks(world: int):
+    """(first layer, second layer) row chunks of a GCN: one piece with one rank (nothing to
+    overlap); otherwise the 256-wide first layer in five pieces of 1/8, 1/8, 1/4, 1/4, 1/4 of the
+    rows and the 64-wide second one in eight equal pieces.  SCORCH_B200_GCN_CHUNKS overrides:
+    "6" (both layers), "4;8" (first; second), or proportions such as "1,1,2,2,2;8"."""
     env = os.environ.get("SCORCH_B200_GCN_CHUNKS")
     if env:
-        return max(1, int(env))
-    return 1 if world == 1 else 8
+        parts = [[int(x) for x in p.split(",")] for p in env.split(";")]
+        parts = [p[0] if len(p) == 1 else p for p in parts]
+        return parts[0], parts[-1]
+    return (1, 1) if world == 1 else ([1, 1, 2, 2, 2], 8)
+
+
+def chunk_offsets(rows: int, spec) -> List[int]:
+    """Row offsets [0, ..., rows] of the chunks: `spec` equal pieces (int) or pieces in the given
+    proportions (sequence).  Every piece holds at least one row where rows allow."""
+    weights = [1] * int(spec) if isinstance(spec, int) else [int(w) for w in spec]
+    if not weights or any(w <= 0 for w in weights):
+        raise ValueError("chunks must be a positive count or a sequence of positive proportions")
+    total, acc, out = sum(weights), 0, [0]
+    for w in weights:
+        acc += w
+        out.append(max(out[-1], -(-rows * acc // total)))
+    out[-1] = rows
+    return out
 
 
 @dataclass
-class ShardedCsr:
-    """One rank's row block of a square CSR matrix, split by operand row chunk."""
-    rank: int
-    world: int
-    bounds: List[int]          # world+1 row bounds of the global matrix
-    chunk_rows: int            # operand rows per rank in one chunk
-    blocks: List[CsrBlock]     # one sub-matrix per chunk, columns in the chunk's gathered layout
-    n_global: int
-    local: CsrBlock            # the unsplit row block with global column indices
-    _buffers: dict = field(default_factory=dict)
+class Split:
+    """A rank's row block split by operand row chunk: chunk c covers rows [offsets[c],
+    offsets[c+1]) of every rank's (padded) block; blocks[c] holds the entries whose column lies
+    there, renumbered to the layout an all-gather of those pieces produces."""
+    offsets: List[int]
+    blocks: List[CsrBlock]
 
     @property
     def chunks(self) -> int:
         return len(self.blocks)
 
+    def rows_of(self, c: int) -> int:
+        return self.offsets[c + 1] - self.offsets[c]
+
+
+@dataclass
+class ShardedCsr:
+    """One rank's row block of a square CSR matrix, split by operand row chunk (one split per
+    layer kind: ``splits[0]`` for the first layer, ``splits[-1]`` for the last)."""
+    rank: int
+    world: int
+    bounds: List[int]          # world+1 row bounds of the global matrix
+    max_rows: int              # rows of the largest block = rows per rank in the padded layout
+    splits: List[Split]
+    n_global: int
+    local: CsrBlock            # the unsplit row block with global column indices
+    _buffers: dict = field(default_factory=dict)
+
     @property
-    def max_rows(self) -> int:
-        """Rows per rank in the padded layout (chunks * chunk_rows >= the largest block)."""
-        return self.chunks * self.chunk_rows
+    def blocks(self) -> List[CsrBlock]:
+        return self.splits[0].blocks
+
+    @property
+    def chunks(self) -> int:
+        return self.splits[0].chunks
 
     @property
     def rows(self) -> int:
@@ -118,18 +164,29 @@ class ShardedCsr:
 
     @staticmethod
     def from_global(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, rank: int, world: int,
-                    n_cols: Optional[int] = None, chunks: Optional[int] = None) -> "ShardedCsr":
+                    n_cols: Optional[int] = None, chunks=None, chunks2=None) -> "ShardedCsr":
+        """``chunks``: row chunks of the first layer, a count or a sequence of proportions;
+        ``chunks2``: the same for the second layer (default: like the first).  With neither,
+        ``default_chunks(world)``."""
         m = pos.numel() - 1
         n_cols = m if n_cols is None else n_cols
         if n_cols != m:
             raise ValueError("sharded layers need a square matrix (features are sharded like rows); "
                              "use row_block / sharded_spmm_replicated for a replicated operand")
         local, bounds = row_block(pos, crd, val, rank, world)
-        chunks = default_chunks(world) if chunks is None else max(1, int(chunks))
+        if chunks is None:
+            chunks, default2 = default_chunks(world)
+            chunks2 = default2 if chunks2 is None else chunks2
+        specs = [chunks, chunks if chunks2 is None else chunks2]
         largest = max(bounds[g + 1] - bounds[g] for g in range(world))
-        chunk_rows = max(1, -(-largest // chunks))
-        blocks = _split_by_chunk(local, bounds, chunk_rows, chunks)
-        return ShardedCsr(rank, world, bounds, chunk_rows, blocks, m, local)
+        splits, seen = [], {}
+        for spec in specs:
+            key = spec if isinstance(spec, int) else tuple(spec)
+            if key not in seen:
+                offsets = chunk_offsets(max(1, largest), spec)
+                seen[key] = Split(offsets, _split_by_chunk(local, bounds, offsets))
+            splits.append(seen[key])
+        return ShardedCsr(rank, world, bounds, max(1, largest), splits, m, local)
 
     def buffer(self, name: str, shape, device) -> torch.Tensor:
         key = (name, tuple(shape))
@@ -140,19 +197,21 @@ class ShardedCsr:
         return buf
 
 
-def _split_by_chunk(local: CsrBlock, bounds: List[int], chunk_rows: int, chunks: int) -> List[CsrBlock]:
-    """Sub-matrix c keeps the entries whose column lies in rows [c*chunk_rows, (c+1)*chunk_rows)
-    of its owner's block, renumbered to the layout an all-gather of those pieces produces.
-    Columns stay ascending within a row (owner, then offset, is the global order)."""
+def _split_by_chunk(local: CsrBlock, bounds: List[int], offsets: List[int]) -> List[CsrBlock]:
+    """Sub-matrix c keeps the entries whose column lies in rows [offsets[c], offsets[c+1]) of its
+    owner's block, renumbered to the layout an all-gather of those pieces produces.  Columns stay
+    ascending within a row (owner, then offset, is the global order)."""
     dev = local.crd.device
-    rows = local.rows
+    rows, chunks = local.rows, len(offsets) - 1
     starts = torch.tensor(bounds[:-1], dtype=torch.int64, device=dev)
+    cuts = torch.tensor(offsets, dtype=torch.int64, device=dev)
     j = local.crd.to(torch.int64)
     owner = torch.bucketize(j, starts, right=True) - 1
     off = j - starts[owner]
     del j
-    c = torch.div(off, chunk_rows, rounding_mode="floor")
-    newcol = (owner * chunk_rows + (off - c * chunk_rows)).to(torch.int32)
+    c = torch.bucketize(off, cuts[1:-1].contiguous(), right=True)
+    width = cuts[1:] - cuts[:-1]
+    newcol = (owner * width[c] + (off - cuts[c])).to(torch.int32)
     del owner, off
     if chunks == 1:
         return [CsrBlock(local.pos, newcol, local.val)]
@@ -167,10 +226,10 @@ def _split_by_chunk(local: CsrBlock, bounds: List[int], chunk_rows: int, chunks:
     del order, newcol
     pos_all = torch.zeros(chunks * rows + 1, dtype=torch.int64, device=dev)
     pos_all[1:] = torch.cumsum(counts, 0)
-    cuts = pos_all[::rows][:chunks + 1].tolist() if rows else [0] * (chunks + 1)
+    ends = pos_all[::rows][:chunks + 1].tolist() if rows else [0] * (chunks + 1)
     out = []
     for ci in range(chunks):
-        e0, e1 = int(cuts[ci]), int(cuts[ci + 1])
+        e0, e1 = int(ends[ci]), int(ends[ci + 1])
         p = (pos_all[ci * rows: ci * rows + rows + 1] - e0).to(torch.int32).contiguous()
         out.append(CsrBlock(p, crd_s[e0:e1], val_s[e0:e1]))
     return out
@@ -279,38 +338,31 @@ class _Gatherer:
                 self.main.wait_event(event)
 
 
-def _chunk_rows(shard: ShardedCsr, c: int):
-    """Local row range whose transform fills piece c of the send buffer."""
-    lo = min(c * shard.chunk_rows, shard.rows)
-    hi = min((c + 1) * shard.chunk_rows, shard.rows)
-    return lo, hi
-
-
-def _pipelined_layer(shard: ShardedCsr, g: _Gatherer, name: str, x_local: torch.Tensor,
+def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x_local: torch.Tensor,
                      weight: Optional[torch.Tensor], out: torch.Tensor, relu: bool,
                      spmm_fn: Callable, lookahead: int, tl: Optional[Timeline], label: str) -> None:
     """out = act(A (x_local W)) over this rank's rows, chunk by chunk (W = None: act(A x))."""
-    S, Rc, dev = shard.chunks, shard.chunk_rows, x_local.device
+    S, dev = split.chunks, x_local.device
     k = out.shape[1]
-    send = shard.buffer(name + "send", (S * Rc, k), dev)
+    send = shard.buffer(name + "send", (shard.max_rows, k), dev)
     pending = []
     tlg = tl if dev.type == "cuda" else None
 
     def produce(c):
-        lo, hi = _chunk_rows(shard, c)
+        lo, hi = min(split.offsets[c], shard.rows), min(split.offsets[c + 1], shard.rows)
         if hi > lo:
             with _span(tlg, "dense_transform"):
                 if weight is not None:
                     torch.matmul(x_local[lo:hi], weight, out=send[lo:hi])
                 else:
                     send[lo:hi].copy_(x_local[lo:hi])
-        pending.append(g.gather(f"{name}recv{c}", send[c * Rc:(c + 1) * Rc]))
+        pending.append(g.gather(f"{name}recv{c}", send[split.offsets[c]:split.offsets[c + 1]]))
 
     def consume(c):
         buf, ev = pending[c]
         g.wait(ev)
         with _span(tlg, label):
-            spmm_fn(shard.blocks[c], buf, out, relu and c == S - 1, c > 0)
+            spmm_fn(split.blocks[c], buf, out, relu and c == S - 1, c > 0)
 
     for c in range(S):
         produce(c)
@@ -333,7 +385,9 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
     k = weight.shape[1] if weight is not None else x_local.shape[1]
     out = torch.empty((shard.rows, k), dtype=torch.float32, device=dev)
     g = _Gatherer(shard, dev, group, timeline)
-    _pipelined_layer(shard, g, f"layer{k}", x_local, weight, out, relu, spmm_fn, lookahead, timeline, "spmm")
+    split = shard.splits[0] if k > 128 else shard.splits[-1]
+    _pipelined_layer(shard, split, g, f"layer{k}", x_local, weight, out, relu, spmm_fn, lookahead, timeline,
+                     "spmm")
     return out
 
 
@@ -355,8 +409,10 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
     g = _Gatherer(shard, dev, group, timeline)
     H = shard.buffer("hidden", (shard.rows, k1), dev)
     out = torch.empty((shard.rows, k2), dtype=torch.float32, device=dev)
-    _pipelined_layer(shard, g, "l1", x_local, W1, H, True, spmm_fn, lookahead, timeline, "spmm_layer1")
-    _pipelined_layer(shard, g, "l2", H, W2, out, False, spmm_fn, lookahead, timeline, "spmm_layer2")
+    _pipelined_layer(shard, shard.splits[0], g, "l1", x_local, W1, H, True, spmm_fn, lookahead, timeline,
+                     "spmm_layer1")
+    _pipelined_layer(shard, shard.splits[-1], g, "l2", H, W2, out, False, spmm_fn, lookahead, timeline,
+                     "spmm_layer2")
     if timeline is not None:
         timeline.steps += 1
     return out
@@ -375,3 +431,76 @@ def gather_rows(shard: ShardedCsr, local: torch.Tensor, group=None) -> torch.Ten
     parts = [buf[g * largest: g * largest + (shard.bounds[g + 1] - shard.bounds[g])]
              for g in range(shard.world)]
     return torch.cat(parts, 0)
+
+
+# ---- SpMV / SpGEMM / independent units ------------------------------------------------------------
+def unit_range(units: int, rank: int, world: int):
+    """Contiguous share [first, last) of `units` independent work items (the (batch, head) pairs
+    of a sparse-attention call) for this rank; shares differ by at most one."""
+    return (units * rank) // world, (units * (rank + 1)) // world
+
+
+def sharded_spmv(block: CsrBlock, x: torch.Tensor, spmv_fn: Optional[Callable] = None) -> torch.Tensor:
+    """This rank's rows of A x for a vector every rank holds (no communication)."""
+    if spmv_fn is not None:
+        return spmv_fn(block, x)
+    from . import kernels as K
+    return K.spmv_csr(block.pos, block.crd, block.val, x)
+
+
+def gather_vector(local: torch.Tensor, bounds: List[int], group=None) -> torch.Tensor:
+    """The row blocks of a sharded vector concatenated on every rank (one all-gather of blocks
+    padded to the largest one)."""
+    world = len(bounds) - 1
+    if world == 1:
+        return local
+    largest = max(bounds[g + 1] - bounds[g] for g in range(world))
+    send = torch.zeros(largest, dtype=local.dtype, device=local.device)
+    send[:local.numel()] = local
+    buf = torch.empty(world * largest, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf, send, group=group)
+    return torch.cat([buf[g * largest: g * largest + bounds[g + 1] - bounds[g]] for g in range(world)])
+
+
+def product_bounds(Apos: torch.Tensor, Acrd: torch.Tensor, Bpos: torch.Tensor, parts: int) -> List[int]:
+    """Row bounds of A that balance the number of scalar products of A B (entry (i, j) of A costs
+    one product per stored entry of row j of B): block g starts at the first row whose running
+    product count reaches g/parts of the total."""
+    m = Apos.numel() - 1
+    blen = (Bpos[1:] - Bpos[:-1]).to(torch.int64)
+    per_entry = blen[Acrd.to(torch.int64)]
+    run = torch.zeros(Acrd.numel() + 1, dtype=torch.int64, device=Acrd.device)
+    run[1:] = torch.cumsum(per_entry, 0)
+    row_run = run[Apos.to(torch.int64)]                  # products before each row
+    total = int(row_run[-1])
+    targets = torch.tensor([(total * g) // parts for g in range(parts)], dtype=torch.int64,
+                           device=Acrd.device)
+    b = torch.searchsorted(row_run.contiguous(), targets, right=False).tolist()
+    return [min(int(x), m) for x in b] + [m]
+
+
+def sharded_spgemm(Ablock: CsrBlock, Bpos, Bcrd, Bval, n: int, group=None,
+                   spgemm_fn: Optional[Callable] = None):
+    """This rank's rows of C = A B (both phases of the SpGEMM on the local row block, B held by
+    every rank).  Returns (Cpos, Ccrd, Cval, offset, total): ``Cpos`` are the rows' pointers into
+    the rank's own arrays (starting at 0); ``offset`` is what to add to make them pointers into
+    the concatenation of all ranks' arrays (the stored entries of the ranks before this one) and
+    ``total`` the entry count of the whole product — from one all-gather of the per-rank counts."""
+    if spgemm_fn is None:
+        from . import kernels as K
+        cpos, ccrd, cval = K.spgemm_csr(Ablock.pos, Ablock.crd, Ablock.val, Bpos, Bcrd, Bval, n)
+    else:
+        cpos, ccrd, cval = spgemm_fn(Ablock, Bpos, Bcrd, Bval, n)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    counts = torch.zeros(world, dtype=torch.int64, device=ccrd.device)
+    mine = torch.tensor([ccrd.numel()], dtype=torch.int64, device=ccrd.device)
+    if world > 1:
+        dist.all_gather_into_tensor(counts, mine, group=group)
+    else:
+        counts[0] = mine[0]
+    counts = counts.tolist()
+    total = sum(counts)
+    if total > 2**31 - 1:
+        raise OverflowError(f"the product has {total} stored entries: global int32 row pointers overflow")
+    return cpos, ccrd, cval, sum(counts[:rank]), total

@@ -30,6 +30,16 @@ class TensorFormat:
     def __str__(self) -> str:
         return ",".join(self.levels)
 
+    def __add__(self, other: "STensor") -> "STensor":
+        """Element-wise sum of two sparse matrices (reference: STensor.__add__)."""
+        from . import ops
+        return ops.elementwise("add", self, other)
+
+    def __mul__(self, other: "STensor") -> "STensor":
+        """Element-wise product of two sparse matrices."""
+        from . import ops
+        return ops.elementwise("mul", self, other)
+
     def __repr__(self) -> str:
         return f"TensorFormat({str(self)!r})"
 

@@ -148,5 +148,23 @@ exec(compile(ast.Module(body=[_fn], type_ignores=[]), "bench_sparse_transformer.
 sm = _ns["_sparse_softmax_csr_vectorized"](csr.crow_indices(), csr.values(), 35)
 put("softmax", pos=pos, val=val, out=sm)
 
+# ---- element-wise CSR (x) CSR multiply and CSR + CSR add (compiler-emitted merge loops) -----------------
+from scorch import STensor  # noqa: E402
+
+# (float32 only: the reference's emitted code for these patterns rejects other value types)
+for name, dtype in (("ewise_f32", np.float32),):
+    A = rand_csr(33, 27, 0.3, dtype, empty_rows=(4, 32))
+    B = rand_csr(33, 27, 0.3, dtype, empty_rows=(4, 9))
+    a_st, b_st = STensor.from_torch(A), STensor.from_torch(B)
+    prod = scorch.einsum("ij,ij->ij", a_st, b_st, format="ds")
+    total = a_st + b_st
+    ap, ac, av = csr_arrays(A)
+    bp, bc, bv = csr_arrays(B)
+    put(name, Apos=ap, Acrd=ac, Aval=av, Bpos=bp, Bcrd=bc, Bval=bv,
+        mul_pos=prod.index.mode_indices[1][0], mul_crd=prod.index.mode_indices[1][1], mul_val=prod.values,
+        mul_format=np.array([str(prod.format)]),
+        add_pos=total.index.mode_indices[1][0], add_crd=total.index.mode_indices[1][1], add_val=total.values,
+        add_format=np.array([str(total.format)]), n=np.array([27]))
+
 np.savez_compressed(os.path.join(HERE, "hotpath_golden.npz"), **out)
 print("wrote", len(out), "arrays;", sum(v.nbytes for v in out.values()), "bytes")

@@ -64,7 +64,7 @@ def test_sharded_gcn_two_gpus(tmp_path, oracle):
     assert ok, (err, bad)
 
 
-@pytest.mark.parametrize("chunks", [1, 3, 8])
+@pytest.mark.parametrize("chunks", [1, 3, 8, [1, 1, 2, 2, 2]])
 def test_chunked_gcn_one_gpu_matches_unchunked(oracle, chunks):
     """World size 1: the row block split into `chunks` sub-matrices, each layer accumulated
     chunk by chunk (heavy rows included), equals the two full-width SpMM launches."""
@@ -73,7 +73,8 @@ def test_chunked_gcn_one_gpu_matches_unchunked(oracle, chunks):
     g = W.gcn_graph(n, mean_deg=30.0, max_deg=9000, seed=1).to("cuda")
     X = W.randn_on((n, 256), seed=2).cuda()
     W1, W2 = W.glorot(256, 256, seed=0).cuda(), W.glorot(256, 64, seed=1).cuda()
-    shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, 0, 1, chunks=chunks)
+    shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, 0, 1, chunks=chunks,
+                                     chunks2=8 if isinstance(chunks, list) else None)
     tl = S.Timeline()
     for _ in range(2):
         out = S.gcn_forward_sharded(shard, X, W1, W2, timeline=tl)
@@ -108,3 +109,58 @@ def test_replicated_operand_row_blocks(oracle):
         assert blk.rows == bounds[rank + 1] - bounds[rank]
         parts.append(S.sharded_spmm_replicated(blk, B))
     assert torch.equal(torch.cat(parts, 0), whole)
+
+
+def _spmv_spgemm_worker(rank, world, port, n, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from scorch_b200 import sharded as S, workloads as W
+        A = W.powerlaw_square(n, mean_nnz=6.0, seed=2).to("cuda")
+        x = W.randn_on((n,), seed=3).cuda()
+        blk, bounds = S.row_block(A.pos, A.crd, A.val, rank, world)
+        y = S.gather_vector(S.sharded_spmv(blk, x), bounds)
+        pb = S.product_bounds(A.pos, A.crd, A.pos, world)
+        ablk, _ = S.row_block(A.pos, A.crd, A.val, rank, world, bounds=pb)
+        cpos, ccrd, cval, offset, total = S.sharded_spgemm(ablk, A.pos, A.crd, A.val, n)
+        torch.cuda.synchronize()
+        torch.save({"y": y.cpu(), "cpos": cpos.cpu(), "ccrd": ccrd.cpu(), "cval": cval.cpu(),
+                    "offset": offset, "total": total}, f"{tmp}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_spmv_and_spgemm_two_gpus(tmp_path, oracle):
+    from scorch_b200 import workloads as W
+    n = 30000
+    tmp = str(tmp_path / "out.pt")
+    mp.spawn(_spmv_spgemm_worker, args=(2, _free_port(), n, tmp), nprocs=2, join=True)
+    parts = [torch.load(f"{tmp}.{r}") for r in range(2)]
+    A = W.powerlaw_square(n, mean_nnz=6.0, seed=2)
+    x = W.randn_on((n,), seed=3)
+    pos, crd, val = A.pos.numpy(), A.crd.numpy(), A.val.numpy()
+    ok, err, bad = oracle.allclose_report(parts[0]["y"].numpy(), oracle.spmv_csr_acc64(pos, crd, val, x.numpy()),
+                                          1e-4, 1e-5)
+    assert ok, (err, bad)
+    assert torch.equal(parts[0]["y"], parts[1]["y"])
+    wpos, wcrd, _ = oracle.spgemm(pos, crd, val, pos, crd, val, n)
+    gpos = np.concatenate([parts[0]["cpos"].numpy()[:-1] + parts[0]["offset"],
+                           parts[1]["cpos"].numpy() + parts[1]["offset"]])
+    assert np.array_equal(gpos, wpos) and parts[0]["total"] == len(wcrd)
+    assert np.array_equal(np.concatenate([p["ccrd"].numpy() for p in parts]), wcrd)
+    want = oracle.spgemm_values_acc64(pos, crd, val, pos, crd, val, n, wpos, wcrd)
+    ok, err, bad = oracle.allclose_report(np.concatenate([p["cval"].numpy() for p in parts]), want, 1e-4, 1e-5)
+    assert ok, (err, bad)
+
+
+def test_sharded_spgemm_single_process_has_no_offset(oracle):
+    from scorch_b200 import sharded as S, workloads as W
+    A = W.powerlaw_square(4000, mean_nnz=5.0, seed=9).to("cuda")
+    blk, bounds = S.row_block(A.pos, A.crd, A.val, 0, 1)
+    cpos, ccrd, cval, offset, total = S.sharded_spgemm(blk, A.pos, A.crd, A.val, 4000)
+    assert offset == 0 and total == ccrd.numel() and bounds == [0, 4000]
+    wpos, wcrd, _ = oracle.spgemm(*(t.cpu().numpy() for t in (A.pos, A.crd, A.val, A.pos, A.crd, A.val)), 4000)
+    assert np.array_equal(cpos.cpu().numpy(), wpos) and np.array_equal(ccrd.cpu().numpy(), wcrd)

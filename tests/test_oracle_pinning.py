@@ -147,3 +147,13 @@ def test_oracle_vs_compiled_reference(oracle, ref_ops):
     assert np.array_equal(cpos, r.storage.index.mode_indices[1][0].numpy())
     assert np.array_equal(ccrd, r.storage.index.mode_indices[1][1].numpy())
     np.testing.assert_allclose(cval, r.storage.value.numpy(), **TOL)
+
+
+@pytest.mark.parametrize("op", ["mul", "add"])
+def test_elementwise_vs_golden(oracle, golden, op):
+    """The reference's compiled merge loops (einsum "ij,ij->ij" and A + B on CSR operands) pin
+    the structure (intersection / union, zeros kept) and the values of the element-wise oracle."""
+    g = golden.case("ewise_f32")
+    pos, crd, val = oracle.csr_ewise(op, g["Apos"], g["Acrd"], g["Aval"], g["Bpos"], g["Bcrd"], g["Bval"])
+    assert np.array_equal(pos, g[f"{op}_pos"]) and np.array_equal(crd, g[f"{op}_crd"])
+    np.testing.assert_allclose(val, g[f"{op}_val"], rtol=1e-6, atol=0)

@@ -42,7 +42,9 @@ def _worker(rank, world, port, n, chunks, tmp):
         X = W.randn_on((n, 24), seed=1)
         W1, W2 = W.glorot(24, 40, seed=0), W.glorot(40, 8, seed=1)
         shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, rank, world, chunks=chunks)
-        assert shard.chunks == chunks and sum(b.nnz for b in shard.blocks) == shard.nnz
+        want_chunks = chunks if isinstance(chunks, int) else len(chunks)
+        assert shard.chunks == want_chunks and sum(b.nnz for b in shard.blocks) == shard.nnz
+        assert sum(b.nnz for b in shard.splits[-1].blocks) == shard.nnz
         r0, r1 = shard.bounds[rank], shard.bounds[rank + 1]
         out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, spmm_fn=_oracle_spmm)
         one = S.sharded_layer(shard, X[r0:r1].contiguous(), W1, relu=True, spmm_fn=_oracle_spmm)
@@ -50,12 +52,12 @@ def _worker(rank, world, port, n, chunks, tmp):
         full, full_one = S.gather_rows(shard, out), S.gather_rows(shard, one)
         if rank == 0:
             torch.save({"out": full, "one": full_one, "bounds": shard.bounds, "max_rows": shard.max_rows,
-                        "chunk_rows": shard.chunk_rows}, tmp)
+                        "offsets": shard.splits[0].offsets}, tmp)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (3, 4)])
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (3, 4), (2, [1, 1, 2, 3])])
 def test_sharded_gcn_matches_single_process(tmp_path, world, chunks):
     from oracle import oracle as O
     from scorch_b200 import sharded as S, workloads as W
@@ -77,7 +79,11 @@ def test_sharded_gcn_matches_single_process(tmp_path, world, chunks):
     nnz = np.diff(pos[np.array(b)])
     assert nnz.max() - nnz.min() <= 2 * np.diff(pos).max()
     largest = max(b[i + 1] - b[i] for i in range(world))
-    assert got["max_rows"] == chunks * got["chunk_rows"] >= largest > (chunks - 1) * got["chunk_rows"] - chunks
+    off = got["offsets"]
+    assert got["max_rows"] == largest == off[-1] and off[0] == 0 and off == sorted(off)
+    if not isinstance(chunks, int):   # pieces in the requested proportions (to rounding)
+        sizes = np.diff(off)
+        assert np.all(np.abs(sizes - largest * np.array(chunks) / sum(chunks)) <= 1)
 
 
 def test_chunk_split_single_process_keeps_every_entry():
@@ -86,17 +92,29 @@ def test_chunk_split_single_process_keeps_every_entry():
     from scorch_b200 import sharded as S, workloads as W
     n = 700
     g = W.gcn_graph(n, mean_deg=5.0, max_deg=200, seed=3)
-    shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, 0, 1, chunks=4)
-    dense = torch.zeros((n, n), dtype=torch.float32)
-    for c, blk in enumerate(shard.blocks):
-        lens = (blk.pos[1:] - blk.pos[:-1]).long()
-        rows = torch.repeat_interleave(torch.arange(n), lens)
-        assert blk.nnz == 0 or int(blk.crd.max()) < shard.chunk_rows
-        d = (blk.crd[1:] - blk.crd[:-1])[rows[1:] == rows[:-1]]
-        assert bool((d > 0).all())
-        dense[rows, blk.crd.long() + c * shard.chunk_rows] += blk.val
+    shard = S.ShardedCsr.from_global(g.pos, g.crd, g.val, 0, 1, chunks=4, chunks2=[1, 2, 4])
+    assert [sp.chunks for sp in shard.splits] == [4, 3]
     want = g.torch_csr().to_dense()
-    assert torch.equal(dense, want)
+    for split in shard.splits:
+        dense = torch.zeros((n, n), dtype=torch.float32)
+        for c, blk in enumerate(split.blocks):
+            lens = (blk.pos[1:] - blk.pos[:-1]).long()
+            rows = torch.repeat_interleave(torch.arange(n), lens)
+            assert blk.nnz == 0 or int(blk.crd.max()) < split.rows_of(c)
+            d = (blk.crd[1:] - blk.crd[:-1])[rows[1:] == rows[:-1]]
+            assert bool((d > 0).all())
+            dense[rows, blk.crd.long() + split.offsets[c]] += blk.val
+        assert torch.equal(dense, want)
+
+
+def test_chunk_offsets():
+    from scorch_b200 import sharded as S
+    assert S.chunk_offsets(100, 4) == [0, 25, 50, 75, 100]
+    assert S.chunk_offsets(10, [1, 1, 2]) == [0, 3, 5, 10]
+    assert S.chunk_offsets(2, 4) == [0, 1, 1, 2, 2]          # more pieces than rows: empty pieces
+    assert S.chunk_offsets(7, 1) == [0, 7]
+    with pytest.raises(ValueError):
+        S.chunk_offsets(7, [1, 0])
 
 
 def test_row_bounds_host_matches_definition():
@@ -106,3 +124,61 @@ def test_row_bounds_host_matches_definition():
     # block g starts at the first row r with pos[r] >= g*nnz/3
     assert b == [0, 4, 4, 8] or b == [0, int(np.searchsorted(pos.numpy(), 10)), int(np.searchsorted(pos.numpy(), 20)), 8]
     assert S.row_bounds(pos, 1) == [0, 8]
+
+
+def _spmv_spgemm_worker(rank, world, port, n, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as O
+        from scorch_b200 import sharded as S, workloads as W
+        A = W.powerlaw_square(n, mean_nnz=5.0, seed=2)
+        x = W.randn_on((n,), seed=3)
+        # SpMV: rows balanced by stored entries, x replicated, y gathered
+        blk, bounds = S.row_block(A.pos, A.crd, A.val, rank, world)
+        spmv = lambda b, v: torch.from_numpy(O.spmv_csr(b.pos.numpy(), b.crd.numpy(), b.val.numpy(), v.numpy()))
+        y = S.gather_vector(S.sharded_spmv(blk, x, spmv_fn=spmv), bounds)
+        # SpGEMM: rows balanced by products, B replicated, pointers offset by the ranks before
+        pb = S.product_bounds(A.pos, A.crd, A.pos, world)
+        ablk, _ = S.row_block(A.pos, A.crd, A.val, rank, world, bounds=pb)
+
+        def spgemm(b, Bp, Bc, Bv, nn):
+            p, c, v = O.spgemm(b.pos.numpy(), b.crd.numpy(), b.val.numpy(), Bp.numpy(), Bc.numpy(), Bv.numpy(), nn)
+            return torch.from_numpy(p), torch.from_numpy(c), torch.from_numpy(v)
+        cpos, ccrd, cval, offset, total = S.sharded_spgemm(ablk, A.pos, A.crd, A.val, n, spgemm_fn=spgemm)
+        torch.save({"y": y, "pb": pb, "cpos": cpos, "ccrd": ccrd, "cval": cval, "offset": offset,
+                    "total": total, "unit_range": S.unit_range(32, rank, world)}, f"{tmp}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_spmv_and_spgemm_match_single_process(tmp_path):
+    from oracle import oracle as O
+    from scorch_b200 import workloads as W
+    n, world = 1200, 2
+    tmp = str(tmp_path / "out.pt")
+    mp.spawn(_spmv_spgemm_worker, args=(world, _free_port(), n, tmp), nprocs=world, join=True)
+    parts = [torch.load(f"{tmp}.{r}") for r in range(world)]
+    A = W.powerlaw_square(n, mean_nnz=5.0, seed=2)
+    x = W.randn_on((n,), seed=3)
+    pos, crd, val = A.pos.numpy(), A.crd.numpy(), A.val.numpy()
+    want_y = O.spmv_csr(pos, crd, val, x.numpy())
+    for p in parts:
+        assert np.array_equal(p["y"].numpy(), want_y)
+    wpos, wcrd, wval = O.spgemm(pos, crd, val, pos, crd, val, n)
+    pb = parts[0]["pb"]
+    assert pb[0] == 0 and pb[-1] == n and parts[1]["pb"] == pb
+    # the ranks' arrays concatenated, pointers offset, are the whole product bit for bit
+    gpos = np.concatenate([parts[0]["cpos"].numpy()[:-1] + parts[0]["offset"],
+                           parts[1]["cpos"].numpy() + parts[1]["offset"]])
+    assert parts[0]["offset"] == 0 and parts[1]["offset"] == parts[0]["ccrd"].numel()
+    assert parts[0]["total"] == parts[1]["total"] == len(wcrd)
+    assert np.array_equal(gpos, wpos)
+    assert np.array_equal(np.concatenate([p["ccrd"].numpy() for p in parts]), wcrd)
+    assert np.array_equal(np.concatenate([p["cval"].numpy() for p in parts]), wval)
+    # products are balanced: each block within one row's worth of half the total
+    lens = np.diff(pos)
+    prods = np.concatenate([[0], np.cumsum(lens[crd])])[pos]
+    assert abs((prods[pb[1]] - prods[0]) - prods[-1] / 2) <= lens[crd].max() * lens.max()
+    assert [p["unit_range"] for p in parts] == [(0, 16), (16, 32)]
