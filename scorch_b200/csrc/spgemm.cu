@@ -16,7 +16,20 @@
 // ascending.  The structure is the symbolic union: a slot whose value cancels to 0 is kept.
 // Row pointers come from a three-kernel exclusive scan in int64, stored as int32 with an
 // overflow check.
+//
+// Values are reproducible bit for bit from run to run.  Several products may land on one output
+// entry and the hardware serves their atomic additions in any order, so floating-point sums are
+// not added as floats: every product is computed exactly in double, scaled by a power of two
+// chosen per output row so that no partial sum can overflow (2^61 / (sum |a| of the row * max |b|)),
+// rounded to a 64-bit integer and added with integer atomics, whose result does not depend on
+// the order.  The total is converted back once per entry.  The rounding step is 2^-61 of the
+// row's bound, far below fp32 (and fp64) resolution of the sum itself.  Rows whose bound is not
+// finite (Inf / NaN operands) are added as floats like before, so those values propagate.
+// Integer dtypes wrap like the reference's and need none of this.
 #include <limits.h>
+#include <string.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -34,6 +47,8 @@ struct WsLayout {
   int* upper;           // m ints: product upper bound per row (saturating)
   int* bin_rows;        // kBins * m ints
   int* row_cnt;         // m ints
+  double* row_scale;    // m doubles: fixed-point scale of each output row (numeric phase)
+  unsigned long long* max_b;  // bit pattern of max |b| over the right operand
   long long* block_sum; // scan temporaries
   int* dense_ctl;       // task prefix, per-row done counters and queue of the dense bin
   unsigned* bitmap;     // workers * words
@@ -44,7 +59,9 @@ struct WsLayout {
 };
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
-static size_t dtype_size(int dtype) { return (dtype == SB_F64 || dtype == SB_I64) ? 8 : 4; }
+// every accumulator slot is 8 bytes: 64-bit fixed point for the float types, the type itself
+// (in the low bytes) for the integer ones
+static size_t dtype_size(int) { return 8; }
 
 static WsLayout ws_layout(void* base, int64_t m, int64_t n, int dtype) {
   WsLayout w;
@@ -55,6 +72,8 @@ static WsLayout ws_layout(void* base, int64_t m, int64_t n, int dtype) {
   w.upper = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4);
   w.bin_rows = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4 * kBins);
   w.row_cnt = reinterpret_cast<int*>(p + off); off += align_up((size_t)m * 4);
+  w.row_scale = reinterpret_cast<double*>(p + off); off += align_up((size_t)m * 8);
+  w.max_b = reinterpret_cast<unsigned long long*>(p + off); off += align_up(8);
   w.block_sum = reinterpret_cast<long long*>(p + off);
   off += align_up((size_t)(ceil_div(m > 0 ? m : 1, 4096) + 1) * 8);
   w.dense_ctl = reinterpret_cast<int*>(p + off); off += align_up((size_t)(2 * kDenseWorkersMax + 8) * 4);
@@ -125,18 +144,62 @@ __device__ __forceinline__ int hash_slot(int c) {
   return (int)(((unsigned)c * 0x9E3779B1u) >> (32 - __builtin_ctz(S)));
 }
 
-// Returns 1 when the key was new.
-template <typename T, int S, bool NUMERIC>
-__device__ __forceinline__ int hash_insert(int* keys, T* vals, int c, T v) {
+// Slot of column c in the table, inserting it when absent (`fresh` = it was).
+template <int S>
+__device__ __forceinline__ int hash_find_or_insert(int* keys, int c, int& fresh) {
   int h = hash_slot<S>(c);
   while (true) {
     const int old = atomicCAS(&keys[h], kEmpty, c);
     if (old == kEmpty || old == c) {
-      if (NUMERIC) atomicAdd(&vals[h], v);
-      return old == kEmpty;
+      fresh += (old == kEmpty);
+      return h;
     }
     h = (h + 1) & (S - 1);
   }
+}
+
+// ---- order-independent accumulation ------------------------------------------------------------
+// An accumulator slot is 8 bytes.  Float types: a 64-bit fixed-point sum of the exactly computed,
+// scaled products (integer atomics: the same bits whatever the order); with `fixed` false (the
+// row's bound is not finite) the slot's low bytes hold a plain T added with float atomics.
+// Integer types: the slot's low bytes hold T, added with wrapping integer atomics.
+typedef unsigned long long Slot;
+
+template <typename T> struct IsFloat { static constexpr bool value = false; };
+template <> struct IsFloat<float> { static constexpr bool value = true; };
+template <> struct IsFloat<double> { static constexpr bool value = true; };
+
+template <typename T>
+__device__ __forceinline__ void acc_add(Slot* slot, T a, T b, double scale, bool fixed) {
+  if constexpr (IsFloat<T>::value) {
+    if (fixed) {
+      const long long q = __double2ll_rn((double)a * (double)b * scale);
+      atomicAdd(slot, (Slot)q);
+    } else {
+      atomicAdd(reinterpret_cast<T*>(slot), a * b);
+    }
+  } else {
+    atomicAdd(reinterpret_cast<T*>(slot), a * b);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T acc_value(Slot v, double inv_scale, bool fixed) {
+  if constexpr (IsFloat<T>::value) {
+    if (fixed) return (T)((double)(long long)v * inv_scale);
+  }
+  T out;
+  memcpy(&out, &v, sizeof(T));
+  return out;
+}
+
+// scale = 2^(61 - exponent of bound); NaN marks "not fixed point"
+__device__ __forceinline__ double scale_for_bound(double bound) {
+  if (!(bound < 1.0e300)) return __longlong_as_double(0x7ff8000000000000LL);  // Inf / NaN
+  if (bound <= 0.0) return 1.0;
+  int e;
+  frexp(bound, &e);                 // bound = f * 2^e, f in [0.5, 1)
+  return ldexp(1.0, 61 - e);        // bound * scale < 2^61
 }
 
 // Bitonic sort of the first P slots (P a power of two <= S) by key, values carried along.
@@ -208,6 +271,7 @@ __device__ __forceinline__ int compact_table(int* keys, T* vals, int tid, int* s
 struct CsrIn {
   const int* Apos; const int* Acrd; const void* Aval;
   const int* Bpos; const int* Bcrd; const void* Bval;
+  const double* row_scale;   // numeric phase, float types: fixed-point scale per output row
 };
 
 // One warp per row (bins 0, 1).  The warp's 4 groups of 8 lanes take alternate entries of the A
@@ -217,18 +281,21 @@ __global__ void __launch_bounds__(128)
 spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
                    const int* __restrict__ Cpos, int* __restrict__ Ccrd, T* __restrict__ Cval) {
   __shared__ int s_keys[4][S];
-  __shared__ T s_vals[4][NUMERIC ? S : 1];
+  __shared__ Slot s_vals[4][NUMERIC ? S : 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * 4 + warp;
   if (r >= nrows) return;
   const int i = __ldg(rows + r);
   int* keys = s_keys[warp];
-  T* vals = s_vals[warp];
+  Slot* vals = s_vals[warp];
   for (int t = lane; t < S; t += 32) {
     keys[t] = kEmpty;
-    if (NUMERIC) vals[t] = T(0);
+    if (NUMERIC) vals[t] = 0;
   }
   __syncwarp();
+  double scale = 1.0;
+  if (NUMERIC && IsFloat<T>::value) scale = in.row_scale[i];
+  const bool fixed = scale == scale;
   const T* Aval = static_cast<const T*>(in.Aval);
   const T* Bval = static_cast<const T*>(in.Bval);
   const int g = lane >> 3, l = lane & 7;
@@ -241,9 +308,8 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
     const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
     for (int pb = bb + l; pb < be; pb += 8) {
       const int c = __ldg(in.Bcrd + pb);
-      T v = T(0);
-      if (NUMERIC) v = a * Bval[pb];
-      fresh += hash_insert<T, S, NUMERIC>(keys, vals, c, v);
+      const int h = hash_find_or_insert<S>(keys, c, fresh);
+      if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
     }
   }
   __syncwarp();
@@ -252,12 +318,13 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
     for (int o = 16; o > 0; o >>= 1) fresh += __shfl_xor_sync(FULL, fresh, o);
     if (lane == 0) row_cnt[i] = fresh;
   } else {
-    const int P = compact_table<T, S, 32, true>(keys, vals, lane, nullptr);
-    bitonic_sort<T, 32, true>(keys, vals, P, lane);
+    const int P = compact_table<Slot, S, 32, true>(keys, vals, lane, nullptr);
+    bitonic_sort<Slot, 32, true>(keys, vals, P, lane);
     const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
+    const double inv = 1.0 / scale;
     for (int t = lane; t < cnt; t += 32) {
       Ccrd[base + t] = keys[t];
-      Cval[base + t] = vals[t];
+      Cval[base + t] = acc_value<T>(vals[t], inv, fixed);
     }
   }
 }
@@ -268,8 +335,8 @@ __global__ void __launch_bounds__(NT)
 spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
                   const int* __restrict__ Cpos, int* __restrict__ Ccrd, T* __restrict__ Cval) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* vals = reinterpret_cast<T*>(smem_raw);                       // S values (numeric only)
-  int* keys = reinterpret_cast<int*>(smem_raw + (NUMERIC ? sizeof(T) * S : 0));
+  Slot* vals = reinterpret_cast<Slot*>(smem_raw);                 // S accumulators (numeric only)
+  int* keys = reinterpret_cast<int*>(smem_raw + (NUMERIC ? sizeof(Slot) * S : 0));
   __shared__ int s_fresh;
   __shared__ int s_scan[NT / 32 + 1];
   const int r = blockIdx.x;
@@ -278,10 +345,13 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int t = tid; t < S; t += NT) {
     keys[t] = kEmpty;
-    if (NUMERIC) vals[t] = T(0);
+    if (NUMERIC) vals[t] = 0;
   }
   if (tid == 0) s_fresh = 0;
   __syncthreads();
+  double scale = 1.0;
+  if (NUMERIC && IsFloat<T>::value) scale = in.row_scale[i];
+  const bool fixed = scale == scale;
   const T* Aval = static_cast<const T*>(in.Aval);
   const T* Bval = static_cast<const T*>(in.Bval);
   const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
@@ -293,9 +363,8 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
     const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
     for (int pb = bb + lane; pb < be; pb += 32) {
       const int c = __ldg(in.Bcrd + pb);
-      T v = T(0);
-      if (NUMERIC) v = a * Bval[pb];
-      fresh += hash_insert<T, S, NUMERIC>(keys, vals, c, v);
+      const int h = hash_find_or_insert<S>(keys, c, fresh);
+      if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
     }
   }
   if (!NUMERIC) {
@@ -306,12 +375,13 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
     if (tid == 0) row_cnt[i] = s_fresh;
   } else {
     __syncthreads();
-    const int P = compact_table<T, S, NT, false>(keys, vals, tid, s_scan);
-    bitonic_sort<T, NT, false>(keys, vals, P, tid);
+    const int P = compact_table<Slot, S, NT, false>(keys, vals, tid, s_scan);
+    bitonic_sort<Slot, NT, false>(keys, vals, P, tid);
     const int base = __ldg(Cpos + i), cnt = __ldg(Cpos + i + 1) - base;
+    const double inv = 1.0 / scale;
     for (int t = tid; t < cnt; t += NT) {
       Ccrd[base + t] = keys[t];
-      Cval[base + t] = vals[t];
+      Cval[base + t] = acc_value<T>(vals[t], inv, fixed);
     }
   }
 }
@@ -350,13 +420,13 @@ __global__ void dense_batch_setup_kernel(const int* __restrict__ rows, int r0, i
 }
 
 template <typename T, bool NUMERIC>
-__device__ __forceinline__ void dense_add_brow(const CsrIn& in, int j, T a, unsigned* bitmap, T* acc,
-                                               int start, int stride) {
+__device__ __forceinline__ void dense_add_brow(const CsrIn& in, int j, T a, unsigned* bitmap, Slot* acc,
+                                               int start, int stride, double scale, bool fixed) {
   const T* Bval = static_cast<const T*>(in.Bval);
   const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
   for (int pb = bb + start; pb < be; pb += stride) {
     const int c = __ldg(in.Bcrd + pb);
-    if (NUMERIC) atomicAdd(&acc[c], a * Bval[pb]);
+    if (NUMERIC) acc_add<T>(acc + c, a, Bval[pb], scale, fixed);
     atomicOr(&bitmap[c >> 5], 1u << (c & 31));
   }
 }
@@ -364,7 +434,7 @@ __device__ __forceinline__ void dense_add_brow(const CsrIn& in, int j, T a, unsi
 template <typename T, bool NUMERIC>
 __global__ void __launch_bounds__(256)
 spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long long words,
-                    unsigned* __restrict__ bitmap_all, T* __restrict__ acc_all, long long n,
+                    unsigned* __restrict__ bitmap_all, Slot* __restrict__ acc_all, long long n,
                     DenseCtl ctl, int* __restrict__ row_cnt, const int* __restrict__ Cpos,
                     int* __restrict__ Ccrd, T* __restrict__ Cval) {
   __shared__ int s_warp[8];
@@ -395,7 +465,10 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
     const int nchunks = __ldg(ctl.task_pref + k + 1) - __ldg(ctl.task_pref + k);
     const int i = __ldg(rows + r0 + k);
     unsigned* bitmap = bitmap_all + (long long)k * words;
-    T* acc = NUMERIC ? acc_all + (long long)k * n : nullptr;
+    Slot* acc = NUMERIC ? acc_all + (long long)k * n : nullptr;
+    double scale = 1.0;
+    if (NUMERIC && IsFloat<T>::value) scale = in.row_scale[i];
+    const bool fixed = scale == scale;
     const int ab = __ldg(in.Apos + i) + chunk * kDenseChunk;
     const int ae = min(__ldg(in.Apos + i + 1), ab + kDenseChunk);
     // warps take A entries; long B rows are put aside for the whole CTA
@@ -412,13 +485,14 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
           mine = false;
         }
       }
-      if (mine) dense_add_brow<T, NUMERIC>(in, j, NUMERIC ? Aval[pa] : T(0), bitmap, acc, lane, 32);
+      if (mine) dense_add_brow<T, NUMERIC>(in, j, NUMERIC ? Aval[pa] : T(0), bitmap, acc, lane, 32, scale, fixed);
     }
     __syncthreads();
     const int nd = min(s_ndefer, kDeferCap);
     for (int q = 0; q < nd; q++) {
       const int pa = s_defer[q];
-      dense_add_brow<T, NUMERIC>(in, __ldg(in.Acrd + pa), NUMERIC ? Aval[pa] : T(0), bitmap, acc, tid, 256);
+      dense_add_brow<T, NUMERIC>(in, __ldg(in.Acrd + pa), NUMERIC ? Aval[pa] : T(0), bitmap, acc, tid, 256,
+                                 scale, fixed);
     }
     // publish this chunk, then find out whether it was the row's last one
     __threadfence();
@@ -463,8 +537,8 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
           bits &= bits - 1;
           const long long c = w * 32 + bit;
           Ccrd[o] = (int)c;
-          Cval[o] = __ldcg(acc + c);
-          acc[c] = T(0);
+          Cval[o] = acc_value<T>(__ldcg(acc + c), 1.0 / scale, fixed);
+          acc[c] = 0;
           o++;
         }
       }
@@ -576,6 +650,42 @@ int exclusive_scan_i32(int n, const int* cnt, int* out, long long* block_sum, lo
   return SB_OK;
 }
 
+// ---- fixed-point scales of the numeric phase (float types) ---------------------------------------
+template <typename T>
+__global__ void spgemm_max_abs_kernel(long long nnz, const T* __restrict__ val, unsigned long long* out) {
+  double mx = 0.0;
+  bool bad = false;
+  for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < nnz;
+       p += (long long)gridDim.x * blockDim.x) {
+    const double v = fabs((double)val[p]);
+    if (!(v < 1.0e300)) bad = true; else mx = fmax(mx, v);
+  }
+  if (bad) mx = __longlong_as_double(0x7ff0000000000000LL);  // +inf: sorts above every finite bit pattern
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(FULL, mx, o));
+  // non-negative doubles order like their bit patterns
+  if ((threadIdx.x & 31) == 0) atomicMax(out, (unsigned long long)__double_as_longlong(mx));
+}
+
+// 8 lanes per row: scale of row i from sum |a| over the row and max |b|.
+template <typename T>
+__global__ void __launch_bounds__(256)
+spgemm_row_scale_kernel(int m, const int* __restrict__ Apos, const T* __restrict__ Aval,
+                        const unsigned long long* __restrict__ max_b, double* __restrict__ row_scale) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = t >> 3;
+  const int l = (int)(t & 7);
+  double s = 0.0;
+  if (row < m) {
+    const int b = __ldg(Apos + row), e = __ldg(Apos + row + 1);
+    for (int p = b + l; p < e; p += 8) s += fabs((double)Aval[p]);
+  }
+  s += __shfl_xor_sync(FULL, s, 4);
+  s += __shfl_xor_sync(FULL, s, 2);
+  s += __shfl_xor_sync(FULL, s, 1);
+  if (l == 0 && row < m) row_scale[row] = scale_for_bound(s * __longlong_as_double((long long)*max_b));
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 template <typename T, bool NUMERIC>
 static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, int64_t n,
@@ -594,7 +704,7 @@ static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, in
 #define SB_CTA_BIN(IDX, SLOTS, THREADS)                                                        \
   if (counts[IDX] > 0) {                                                                      \
     constexpr int S = SLOTS;                                                                  \
-    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(T) : 0);                \
+    const size_t smem = (size_t)S * 4 + (NUMERIC ? (size_t)S * sizeof(Slot) : 0);             \
     auto k = spgemm_cta_kernel<T, S, THREADS, NUMERIC>;                                       \
     SB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     k<<<(unsigned)counts[IDX], THREADS, smem, st>>>(rows0 + (long long)IDX * m, (int)counts[IDX], \
@@ -613,7 +723,7 @@ static int launch_bins(const WsLayout& w, const long long* counts, int64_t m, in
       dense_batch_setup_kernel<<<1, 32, 0, st>>>(rows0 + 5 * m, (int)r0, nb, in.Apos, ctl);
       SB_LAUNCH_CHECK("dense_batch_setup_kernel");
       spgemm_dense_kernel<T, NUMERIC><<<grid, 256, 0, st>>>(
-          rows0 + 5 * m, (int)r0, nb, in, w.words, w.bitmap, static_cast<T*>(w.dense_acc),
+          rows0 + 5 * m, (int)r0, nb, in, w.words, w.bitmap, static_cast<Slot*>(w.dense_acc),
           (long long)n, ctl, w.row_cnt, Cpos, Ccrd, Cval);
       SB_LAUNCH_CHECK("spgemm_dense_kernel");
     }
@@ -679,7 +789,7 @@ int sb_spgemm_symbolic(int64_t m, int64_t kb, int64_t n, const int32_t* Apos, co
   long long counts[kBins];
   for (int b = 0; b < kBins; b++) counts[b] = cursors[b];
   if (counts[kBins - 1] > 0) SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
-  CsrIn in{Apos, Acrd, nullptr, Bpos, Bcrd, nullptr};
+  CsrIn in{Apos, Acrd, nullptr, Bpos, Bcrd, nullptr, nullptr};
   rc = launch_bins<float, false>(w, counts, m, n, in, nullptr, nullptr, nullptr, st);
   if (rc != SB_OK) return rc;
   rc = exclusive_scan_i32((int)m, w.row_cnt, Cpos, w.block_sum, w.hdr + 8, st);
@@ -724,7 +834,26 @@ int sb_spgemm_numeric(int dtype, int64_t m, int64_t kb, int64_t n, const int32_t
     SB_CUDA(cudaMemsetAsync(w.bitmap, 0, (size_t)w.workers * w.words * 4, st));
     SB_CUDA(cudaMemsetAsync(w.dense_acc, 0, (size_t)w.workers * (size_t)n * dtype_size(dtype), st));
   }
-  CsrIn in{Apos, Acrd, Aval, Bpos, Bcrd, Bval};
+  CsrIn in{Apos, Acrd, Aval, Bpos, Bcrd, Bval, w.row_scale};
+  if (dtype == SB_F32 || dtype == SB_F64) {
+    long long bnnz = 0;   // stored entries of B = its last row pointer
+    SB_CUDA(cudaMemcpyAsync(&bnnz, Bpos + kb, 4, cudaMemcpyDeviceToHost, st));
+    SB_CUDA(cudaMemsetAsync(w.max_b, 0, 8, st));
+    SB_CUDA(cudaStreamSynchronize(st));
+    bnnz &= 0xffffffffLL;
+    if (bnnz > 0) {
+      const unsigned blocks = (unsigned)std::min<long long>(ceil_div(bnnz, 256), 8LL * sm_count());
+      if (dtype == SB_F32) spgemm_max_abs_kernel<float><<<blocks, 256, 0, st>>>(bnnz, (const float*)Bval, w.max_b);
+      else spgemm_max_abs_kernel<double><<<blocks, 256, 0, st>>>(bnnz, (const double*)Bval, w.max_b);
+      SB_LAUNCH_CHECK("spgemm_max_abs_kernel");
+    }
+    const unsigned grid = (unsigned)ceil_div(m * 8, 256);
+    if (dtype == SB_F32)
+      spgemm_row_scale_kernel<float><<<grid, 256, 0, st>>>((int)m, Apos, (const float*)Aval, w.max_b, w.row_scale);
+    else
+      spgemm_row_scale_kernel<double><<<grid, 256, 0, st>>>((int)m, Apos, (const double*)Aval, w.max_b, w.row_scale);
+    SB_LAUNCH_CHECK("spgemm_row_scale_kernel");
+  }
   switch (dtype) {
     case SB_F32:
       return launch_bins<float, true>(w, counts, m, n, in, Cpos, Ccrd, (float*)Cval, st);

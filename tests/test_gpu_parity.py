@@ -409,6 +409,46 @@ def test_spgemm_all_bins_vs_oracle(oracle):
     assert np.array_equal(ccrd.cpu().numpy(), wcrd)
     want = oracle.spgemm_values_acc64(pos, crd, val, pos, crd, val, 60000, wpos, wcrd)
     assert_close(oracle, cval, want, "spgemm values")
+    # reproducible to the last bit, like the reference: sums are accumulated order-independently
+    for _ in range(2):
+        _, _, again = K.spgemm_csr(dev(pos), dev(crd), dev(val), dev(pos), dev(crd), dev(val), 60000)
+        assert torch.equal(cval, again)
+    # a denser product (many products per output entry) in float64 as well
+    B = W.powerlaw_square(3000, mean_nnz=60.0, seed=5)
+    bp, bc = B.pos.numpy(), B.crd.numpy()
+    for dtype, tol in ((np.float32, (RTOL, ATOL)), (np.float64, (1e-12, 1e-13))):
+        bv = B.val.numpy().astype(dtype)
+        p1, c1, v1 = K.spgemm_csr(dev(bp), dev(bc), dev(bv), dev(bp), dev(bc), dev(bv), 3000)
+        p2, c2, v2 = K.spgemm_csr(dev(bp), dev(bc), dev(bv), dev(bp), dev(bc), dev(bv), 3000)
+        assert torch.equal(v1, v2) and torch.equal(c1, c2)
+        w_pos, w_crd, _ = oracle.spgemm(bp, bc, bv, bp, bc, bv, 3000)
+        assert np.array_equal(p1.cpu().numpy(), w_pos) and np.array_equal(c1.cpu().numpy(), w_crd)
+        if dtype == np.float32:
+            w64 = oracle.spgemm_values_acc64(bp, bc, bv, bp, bc, bv, 3000, w_pos, w_crd)
+            ok, err, bad = oracle.allclose_report(v1.cpu().numpy(), w64, *tol)
+            assert ok, (err, bad)
+            assert len(w_crd) < 0.7 * int(np.diff(bp)[bc].sum())   # really several products per entry
+        else:
+            _, _, w = oracle.spgemm(bp, bc, bv, bp, bc, bv, 3000)
+            np.testing.assert_allclose(v1.cpu().numpy(), w, rtol=tol[0], atol=tol[1])
+
+
+def test_spgemm_non_finite_operands_propagate():
+    """Rows that touch an infinite or NaN operand are added as plain floats, so the non-finite
+    values reach the entries they belong to; the other rows are unaffected."""
+    from scorch_b200 import kernels as K
+    Apos, Acrd, Aval = random_csr(40, 30, np.random.default_rng(1).integers(1, 6, 40), seed=2)
+    Bpos, Bcrd, Bval = random_csr(30, 50, np.random.default_rng(3).integers(1, 6, 30), seed=4)
+    clean = K.spgemm_csr(dev(Apos), dev(Acrd), dev(Aval), dev(Bpos), dev(Bcrd), dev(Bval), 50)[2].cpu().numpy()
+    Aval2 = Aval.copy()
+    Aval2[Apos[7]] = np.inf            # first entry of row 7
+    cpos, ccrd, cval = K.spgemm_csr(dev(Apos), dev(Acrd), dev(Aval2), dev(Bpos), dev(Bcrd), dev(Bval), 50)
+    cpos, cval = cpos.cpu().numpy(), cval.cpu().numpy()
+    row7 = slice(cpos[7], cpos[8])
+    assert not np.isfinite(cval[row7]).all()
+    keep = np.ones(len(cval), bool)
+    keep[row7] = False
+    assert np.array_equal(cval[keep], clean[keep])
 
 
 def test_spgemm_rectangular_and_empty(oracle):
