@@ -30,16 +30,6 @@ class TensorFormat:
     def __str__(self) -> str:
         return ",".join(self.levels)
 
-    def __add__(self, other: "STensor") -> "STensor":
-        """Element-wise sum of two sparse matrices (reference: STensor.__add__)."""
-        from . import ops
-        return ops.elementwise("add", self, other)
-
-    def __mul__(self, other: "STensor") -> "STensor":
-        """Element-wise product of two sparse matrices."""
-        from . import ops
-        return ops.elementwise("mul", self, other)
-
     def __repr__(self) -> str:
         return f"TensorFormat({str(self)!r})"
 
@@ -237,6 +227,16 @@ class STensor:
         if t.layout != torch.strided:
             t = t.to_dense()
         return STensor.from_torch(t, name=self.name)
+
+    def __add__(self, other: "STensor") -> "STensor":
+        """Element-wise sum of two sparse matrices (reference: STensor.__add__)."""
+        from . import ops
+        return ops.elementwise("add", self, other)
+
+    def __mul__(self, other: "STensor") -> "STensor":
+        """Element-wise product of two sparse matrices."""
+        from . import ops
+        return ops.elementwise("mul", self, other)
 
     def __repr__(self) -> str:
         return f"STensor(shape={self.shape}, format='{self.format}', dtype={self.dtype}, nnz={self.nnz()})"
