@@ -113,7 +113,7 @@ def test_spmm_many_short_rows(oracle, k):
     lens[[3, 40, 41, 500, 1002]] = [65, 300, 64, 1024, 97]
     lens[[7, 600]] = [T + 9, 2 * T + 100]
     pos, crd, val = random_csr(m, n, lens, seed=200 + k)
-    assert len(crd) < 24 * m
+    assert len(crd) < 24 * m            # below the short-row threshold for every width
     val = (val / np.sqrt(np.repeat(np.maximum(lens, 1), lens))).astype(np.float32)
     B = rng.standard_normal((n, k)).astype(np.float32)
     bias = rng.standard_normal(k).astype(np.float32)
