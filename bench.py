@@ -228,7 +228,7 @@ class SparseAttention(Workload):
                           else P.attention_plan(self.pos, self.crd, self.d, self.d))
         self.block_plan = None if no_blocks or self.attn_plan else P.attention_block_plan(self.pos, self.crd)
         if self.attn_plan:
-            self.kernels = ("sddmm_kernel", "attn_block_kernel", "spmm_rows_kernel")
+            self.kernels = ("attn_scattered_kernel", "attn_block_kernel")
         else:
             self.kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
         self.scores = (None if self.attn_plan else
@@ -249,7 +249,7 @@ class SparseAttention(Workload):
     def run_info(self):
         bp = self.attn_plan or self.block_plan
         return {"units_this_rank": self.units,
-                "path": ("one attention call (blocks on tensor cores with running softmax; scores not stored)"
+                "path": ("one attention call (scattered entries and blocks share a running softmax; scores not stored)"
                          if self.attn_plan else "sddmm, row softmax, spmm"),
                 "blocks_16x16": bp.blocks if bp else 0,
                 "entries_outside_blocks": bp.rem_nnz if bp else self.nnz}
@@ -262,14 +262,13 @@ class SparseAttention(Workload):
             rem, blocks = self.attn_plan.rem_nnz, self.attn_plan.blocks
             rem_idx = (s + 1) * 4 + 2 * rem * 4          # rem_pos, rem_ent, crd of the listed entries
             return {
-                # scores of the remaining entries: index lists, mask values, Q and K in, scores out
-                "sddmm_kernel": rem_idx + rem * 4 + u * (2 * s * d * 4 + rem * 4),
+                # scattered entries: index lists, mask values, Q, K and V in; unnormalised O and
+                # the rows' (maximum, sum) out
+                "attn_scattered_kernel": rem_idx + rem * 4 + u * (4 * s * d * 4 + s * 8),
                 # blocks: plan (column, first entry and mask per block row), mask values of the block
-                # entries, Q, K, V in, O out, remaining scores in / probabilities out
+                # entries, Q, K, V, unnormalised O and (maximum, sum) in, O out
                 "attn_block_kernel": blocks * (4 + 64 + 64) + (nnz - rem) * 4
-                                     + u * (4 * s * d * 4 + 2 * rem * 4),
-                # P V of the remaining entries: index lists, probabilities and V in, O in and out
-                "spmm_rows_kernel": rem_idx + u * (rem * 4 + 3 * s * d * 4),
+                                     + u * (5 * s * d * 4 + s * 8),
             }
         return {
             "sddmm_kernel": idx + nnz * 4 + u * (2 * s * d * 4 + nnz * 4),
@@ -282,9 +281,9 @@ class SparseAttention(Workload):
         if ev is not None:
             ev[0].record()
         if self.attn_plan:
-            # the attention call, kernel by kernel so that each can be timed (stages 1, 2, 4 of
-            # kernels.sparse_attention_csr; together they are the default stages=7 call)
-            for j, stage in enumerate((1, 2, 4)):
+            # the attention call, kernel by kernel so that each can be timed (stages 1 and 2 of
+            # kernels.sparse_attention_csr; together they are the default stages=3 call)
+            for j, stage in enumerate((1, 2)):
                 K.sparse_attention_csr(self.pos, self.crd, self.mval, Q, Km, V, attn_plan=self.attn_plan,
                                        out=self.out, stages=stage)
                 if ev is not None:
@@ -305,7 +304,7 @@ class SparseAttention(Workload):
     def launches_per_step(self):
         # with a block plan the SDDMM and SpMM stages of the three-operator path are two launches
         # each (tensor-core kernel over the dense blocks + gather kernel over the other entries)
-        return 5 if self.block_plan else 3
+        return 2 if self.attn_plan else (5 if self.block_plan else 3)
 
     def e2e_step(self):
         # the public host-tensor call: pinned Q, K, V in, pinned O out, copies inside

@@ -251,31 +251,30 @@ SB_API int sb_csr_row_softmax_f32(int64_t m, int64_t nnz, const int32_t* pos, co
  *           give zero rows of O.
  * An attention plan splits the mask once into the aligned 16x16 blocks that hold at least
  * SB_ATTN_MIN_BLOCK_ENTRIES stored entries (with a mask of the stored columns per row) and a
- * CSR list of the remaining entries.  The blocks run on the tensor cores (TF32x3, fp32-level
- * accuracy) with a running row softmax; the remaining entries go through the gather kernels
- * with their scores in `scratch`.
+ * CSR list of the remaining (scattered) entries.  A call runs two kernels: a gather kernel over
+ * the scattered entries that keeps a running row softmax and leaves, per row, the unnormalised
+ * output in O and (maximum, sum) in `scratch`; then the block kernel, which continues from those
+ * on the tensor cores (TF32x3, fp32-level accuracy) over the row's blocks and writes O / sum.
  *   sb_attn_plan_build   : synchronises; returns the number of blocks and of remaining entries,
  *                          which the attention call takes back.  A mask without blocks is valid
  *                          (everything is "remaining").
  *   sb_sparse_attention_csr_f32 : d (head dimension of Q, K and V) in {32, 64}; Q/K/V 32-byte
  *                          aligned with row pitches and batch strides multiples of 8, O 16-byte
  *                          aligned with pitch and stride multiples of 4; scratch of
- *                          sb_sparse_attention_scratch_bytes(rem_nnz, batch) bytes.
- *                          `stages` is SB_ATTN_ALL_STAGES, or a subset of the three kernels for
- *                          callers that time or schedule them one by one: they must run in the
- *                          order scores of the remaining entries -> blocks -> P V of the
- *                          remaining entries, with the same arguments and scratch.
+ *                          sb_sparse_attention_scratch_bytes(m, rem_nnz, batch) bytes.
+ *                          `stages` is SB_ATTN_ALL_STAGES, or one of the two kernels for callers
+ *                          that time or schedule them one by one: they must run in the order
+ *                          scattered entries -> blocks, with the same arguments, O and scratch.
  * -------------------------------------------------------------------------------------------- */
 #define SB_ATTN_MIN_BLOCK_ENTRIES 64
-#define SB_ATTN_STAGE_REMAINDER_SCORES 1
+#define SB_ATTN_STAGE_SCATTERED 1
 #define SB_ATTN_STAGE_BLOCKS 2
-#define SB_ATTN_STAGE_REMAINDER_PV 4
-#define SB_ATTN_ALL_STAGES 7
+#define SB_ATTN_ALL_STAGES 3
 SB_API size_t sb_attn_plan_bytes(int64_t m, int64_t nnz);
 SB_API int sb_attn_plan_build(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
                               const int32_t* crd, void* plan, size_t plan_bytes,
                               int64_t* blocks_host, int64_t* rem_nnz_host, void* stream);
-SB_API size_t sb_sparse_attention_scratch_bytes(int64_t rem_nnz, int64_t batch);
+SB_API size_t sb_sparse_attention_scratch_bytes(int64_t m, int64_t rem_nnz, int64_t batch);
 SB_API int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz,
                                        const int32_t* pos, const int32_t* crd,
                                        const float* mask_val, const float* Q, int64_t ldq,

@@ -58,7 +58,7 @@ SIGNATURES = {
     "sb_attn_plan_bytes": (_sz, [_i64, _i64]),
     "sb_attn_plan_build": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _sz, C.POINTER(_i64),
                                   C.POINTER(_i64), _ptr]),
-    "sb_sparse_attention_scratch_bytes": (_sz, [_i64, _i64]),
+    "sb_sparse_attention_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "sb_sparse_attention_csr_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                            _i64, _ptr, _i64, _f32, _ptr, _i64, _i64, _i64, _i64, _i64,
                                            _i64, _ptr, _i64, _i64, _ptr, _sz, _int, _ptr]),

@@ -8,16 +8,16 @@
 //     stored blocks of a band and the half-filled ones along its edges), each with a 16-bit mask
 //     of the stored columns per row, and
 //   * a CSR list of the remaining entries (the scattered ones).
-// A call then runs three kernels:
-//   1. the gather SDDMM over the remaining entries (columns from the plan's compact copy),
-//      scores into a compact scratch array;
-//   2. attn_block_kernel, one warp per 16 mask rows: for every block of the row block
-//      S = Q K^T on the tensor cores, entries that are not stored masked to -inf, a running
-//      row maximum / sum (started from the scratch scores of the same rows), P = exp(S - max),
-//      O += P V on the tensor cores; at the end O / sum is written and the scratch scores of
-//      the rows are replaced by their probabilities.  The scores of the blocks never leave the
-//      registers;
-//   3. the gather SpMM over the remaining entries, adding their P V terms to O.
+// A call then runs two kernels:
+//   1. attn_scattered_kernel over the remaining entries, a lane group per row: gather the K row,
+//      dot product with the row's Q (held in registers), running row maximum / sum, gather the V
+//      row and accumulate exp(score - max) V.  Per row it leaves the unnormalised sum in O and
+//      (max, sum) in a small scratch array; no score is written anywhere;
+//   2. attn_block_kernel, one warp per 16 mask rows, which starts its running maximum / sum and
+//      its O accumulators from what kernel 1 left for the same rows and continues over the
+//      blocks of the row block: S = Q K^T on the tensor cores, entries that are not stored masked
+//      to -inf, P = exp(S - max), O += P V on the tensor cores; at the end O / sum is written.
+//      The scores of the blocks never leave the registers.
 // Arithmetic of the blocks: mma.sync m16n8k8 TF32 with the 3xTF32 split (fp32-level accuracy).
 #include <math.h>
 
@@ -239,10 +239,13 @@ struct AttnArgs {
   const float* K;
   const float* V;
   float* O;
-  float* rem;             // [batch][rem_nnz]: scores of the remainder in, their probabilities out
+  float2* stats;          // [batch][m]: (running maximum in log2 units, sum) of each row's scattered entries
+  int has_rem;            // the scattered-entry kernel ran: O and stats hold its results
+  const int* rem_ent;     // entry index in the mask of each scattered entry (for its mask value)
+  const int* rem_crd;     // its column
   unsigned ldq, ldk, ldv;
   long long ldo;
-  long long stride_q, stride_k, stride_v, stride_o, stride_rem;
+  long long stride_q, stride_k, stride_v, stride_o;
   float scale;
 };
 
@@ -272,6 +275,106 @@ __device__ __forceinline__ Float8 ldg8(const float* p) {
   return r;
 }
 
+// ---- the scattered entries -----------------------------------------------------------------------
+// L = d / 8 lanes per mask row (a lane holds 8 features of the row's Q and 8 columns of its
+// output), 32 / L rows per warp.  A group walks its row's scattered entries two at a time: K and
+// V rows of both entries are gathered together (four 256-bit loads in flight per lane), the
+// partial dot products are summed across the group's lanes, and the row's running maximum, sum
+// and unnormalised output are updated once per pair.  Scores are in log2 units like the block
+// kernel's.  The trip count is the longest row of the warp; finished groups idle.
+constexpr int kScatWarps = 8;
+template <int L>
+__global__ void __launch_bounds__(kScatWarps * 32, 4)
+attn_scattered_kernel(AttnArgs a) {
+  constexpr int G = 32 / L;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane / L, l = lane % L;
+  const int row = (blockIdx.x * kScatWarps + warp) * G + g;
+  if ((blockIdx.x * kScatWarps + warp) * G >= a.m) return;
+  const long long bz = blockIdx.y;
+  const float* K = a.K + bz * a.stride_k + 8 * l;
+  const float* V = a.V + bz * a.stride_v + 8 * l;
+  const float scale = a.scale * 1.4426950408889634f;
+  const float* mask_val = (a.mask_val && !__ldg(a.mask_is_ones)) ? a.mask_val : nullptr;
+  const bool live = row < a.m;
+  int b = 0, e = 0;
+  Float8 q;
+#pragma unroll
+  for (int i = 0; i < 8; i++) q.v[i] = 0.f;
+  if (live) {
+    b = __ldg(a.rem_pos + row);
+    e = __ldg(a.rem_pos + row + 1);
+    q = ldg8(a.Q + bz * a.stride_q + (size_t)((unsigned long long)(unsigned)row * a.ldq) + 8 * l);
+  }
+  const int longest = __reduce_max_sync(FULL, e - b);
+  float M = -INFINITY, Ls = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  // the group's next L entries: column and mask value, one per lane, a chunk ahead
+  int next_j = 0;
+  float next_w = 1.f;
+  if (b + l < e) {
+    next_j = ld_stream(a.rem_crd + b + l);
+    if (mask_val) next_w = __ldg(mask_val + ld_stream(a.rem_ent + b + l));
+  }
+#pragma unroll 1
+  for (int q0 = 0; q0 < longest; q0 += L) {
+    const int p0 = b + q0;
+    const int my_j = next_j;
+    const float my_w = next_w;
+    if (p0 + L + l < e) {
+      next_j = ld_stream(a.rem_crd + p0 + L + l);
+      if (mask_val) next_w = __ldg(mask_val + ld_stream(a.rem_ent + p0 + L + l));
+    }
+    const int cnt = e - p0;                       // entries this group still has (may be <= 0)
+    const int most = min(L, longest - q0);        // warp-uniform
+#pragma unroll 1
+    for (int t0 = 0; t0 < most; t0 += 2) {
+      Float8 kv[2], vv[2];
+      float w[2];
+      bool ok[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int t = t0 + u;
+        const unsigned j = (unsigned)__shfl_sync(FULL, my_j, t & (L - 1), L);
+        w[u] = __shfl_sync(FULL, my_w, t & (L - 1), L);
+        ok[u] = t < cnt && t < L;
+        if (ok[u]) {
+          kv[u] = ldg8(K + (size_t)((unsigned long long)j * a.ldk));
+          vv[u] = ldg8(V + (size_t)((unsigned long long)j * a.ldv));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; i++) kv[u].v[i] = vv[u].v[i] = 0.f;
+        }
+      }
+      float sc[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) d = fmaf(q.v[i], kv[u].v[i], d);
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) d += __shfl_xor_sync(FULL, d, o);
+        sc[u] = ok[u] ? d * scale * w[u] : -INFINITY;
+      }
+      const float nm = fmaxf(M, fmaxf(sc[0], sc[1]));
+      const float ms = (nm == -INFINITY) ? 0.f : nm;
+      const float alpha = attn_exp2(M - ms);      // 0 while the row has seen no entry
+      const float p0e = attn_exp2(sc[0] - ms), p1e = attn_exp2(sc[1] - ms);
+      M = nm;
+      Ls = Ls * alpha + p0e + p1e;
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[i] = fmaf(p1e, vv[1].v[i], fmaf(p0e, vv[0].v[i], acc[i] * alpha));
+    }
+  }
+  if (live) {
+    float* orow = a.O + bz * a.stride_o + (long long)row * a.ldo + 8 * l;
+    *reinterpret_cast<float4*>(orow) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(orow + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (l == 0) a.stats[bz * a.m + row] = make_float2(M, Ls);
+  }
+}
+
 // One warp per row block.  Thread (g, t) = (lane / 4, lane % 4) owns rows g and g+8 of the row
 // block in every fragment.  Layouts (see mma_tf32.cuh):
 //   S = Q K^T : A = Q rows, B column g of n-tile n = K row 8n+g; the feature index is permuted so
@@ -299,68 +402,36 @@ attn_block_kernel(AttnArgs a) {
   const float* K = a.K + bz * a.stride_k;
   const float* V = a.V + bz * a.stride_v;
   float* O = a.O + bz * a.stride_o;
-  float* rem = a.rem + bz * a.stride_rem;
   const int i0 = rb * 16;
   const int kb = __ldg(a.rb_ptr + rb), ke = __ldg(a.rb_ptr + rb + 1);
   const float scale = a.scale * 1.4426950408889634f;  // scores are kept in log2 units: exp2 below
   const float* mask_val = (a.mask_val && !__ldg(a.mask_is_ones)) ? a.mask_val : nullptr;
 
-  // running maximum M and (per-thread partial) sum L of both rows, started from the rows'
-  // remainder scores: the 4 lanes of a row take them in chunks of 32 (8 independent loads per
-  // lane and row), each lane keeping a running (max, sum) pair; the pairs are merged at the end
+  // running maximum M, (per-thread partial) sum L and output accumulators of both rows continue
+  // from what the scattered-entry kernel left for them (the row's sum lives on lane t = 0)
   float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.f, 0.f};
-  int qb[2], qe[2];
-#pragma unroll
-  for (int r = 0; r < 2; r++) {
-    const int row = i0 + g + 8 * r;
-    qb[r] = qe[r] = 0;
-    if (row < a.m) {
-      qb[r] = __ldg(a.rem_pos + row);
-      qe[r] = __ldg(a.rem_pos + row + 1);
-    }
-  }
-  const int rem_len = __reduce_max_sync(FULL, max(qe[0] - qb[0], qe[1] - qb[1]));
-#pragma unroll 1
-  for (int c0 = 0; c0 < rem_len; c0 += 32) {
-    float v[2][8];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int q = qb[r] + c0 + 4 * i + t;
-        v[r][i] = (q < qe[r]) ? rem[q] * scale : -INFINITY;
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      float cm = v[r][0];
-#pragma unroll
-      for (int i = 1; i < 8; i++) cm = fmaxf(cm, v[r][i]);
-      const float nm = fmaxf(M[r], cm);
-      const float ms = (nm == -INFINITY) ? 0.f : nm;
-      float sum = L[r] * attn_exp2(M[r] - ms);
-#pragma unroll
-      for (int i = 0; i < 8; i++) sum += attn_exp2(v[r][i] - ms);
-      M[r] = nm;
-      L[r] = sum;
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < 2; r++) {
-#pragma unroll
-    for (int off = 1; off <= 2; off <<= 1) {
-      const float om = __shfl_xor_sync(FULL, M[r], off), os = __shfl_xor_sync(FULL, L[r], off);
-      const float nm = fmaxf(M[r], om);
-      const float ms = (nm == -INFINITY) ? 0.f : nm;
-      L[r] = L[r] * attn_exp2(M[r] - ms) + os * attn_exp2(om - ms);
-      M[r] = nm;
-    }
-    if (t != 0) L[r] = 0.f;  // from here on L is a per-lane partial sum again
-  }
-
   float o[KT][4];
 #pragma unroll
   for (int u = 0; u < KT; u++) o[u][0] = o[u][1] = o[u][2] = o[u][3] = 0.f;
+  if (a.has_rem) {
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const int row = i0 + g + 8 * r;
+      if (row >= a.m) continue;
+      const float2 st = __ldg(a.stats + bz * a.m + row);
+      M[r] = st.x;
+      L[r] = (t == 0) ? st.y : 0.f;
+      const float* orow = O + (long long)row * a.ldo;
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+#pragma unroll
+        for (int u = 0; u < KT; u += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(orow + (2 * t + e) * KT + u);
+          o[u][2 * r + e] = x.x; o[u + 1][2 * r + e] = x.y; o[u + 2][2 * r + e] = x.z; o[u + 3][2 * r + e] = x.w;
+        }
+      }
+    }
+  }
 
   if (kb < ke) {  // (row blocks with blocks are complete: all 16 rows exist)
     {
@@ -571,16 +642,13 @@ attn_block_kernel(AttnArgs a) {
     }
   }
 
-  // O / sum; the remainder scores of the rows become probabilities (their P V terms are added
-  // by the gather kernel that follows)
-  float fin_ms[2], fin_inv[2];
+  // O / sum
 #pragma unroll
   for (int r = 0; r < 2; r++) {
     float sum = L[r];
     sum += __shfl_xor_sync(FULL, sum, 1);
     sum += __shfl_xor_sync(FULL, sum, 2);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    const float ms = (M[r] == -INFINITY) ? 0.f : M[r];
     const int row = i0 + g + 8 * r;
     if (row < a.m) {
       float* orow = O + (long long)row * a.ldo;
@@ -592,28 +660,6 @@ attn_block_kernel(AttnArgs a) {
                                        o[u + 2][2 * r + e] * inv, o[u + 3][2 * r + e] * inv);
           *reinterpret_cast<float4*>(orow + (2 * t + e) * KT + u) = x;
         }
-      }
-    }
-    fin_ms[r] = ms;
-    fin_inv[r] = inv;
-  }
-#pragma unroll 1
-  for (int c0 = 0; c0 < rem_len; c0 += 32) {
-    float v[2][8];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int q = qb[r] + c0 + 4 * i + t;
-        v[r][i] = (q < qe[r]) ? rem[q] : 0.f;
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int q = qb[r] + c0 + 4 * i + t;
-        if (q < qe[r]) rem[q] = attn_exp2(v[r][i] * scale - fin_ms[r]) * fin_inv[r];
       }
     }
   }
@@ -678,11 +724,11 @@ int sb_attn_plan_build(int64_t m, int64_t n, int64_t nnz, const int32_t* pos, co
   return SB_OK;
 }
 
-// scratch: 256 bytes of flags, then [batch][rem_nnz] scores of the remaining entries
-size_t sb_sparse_attention_scratch_bytes(int64_t rem_nnz, int64_t batch) {
-  if (rem_nnz < 0) rem_nnz = 0;
+// scratch: 256 bytes of flags, then [batch][m] (maximum, sum) pairs of the rows' scattered entries
+size_t sb_sparse_attention_scratch_bytes(int64_t m, int64_t rem_nnz, int64_t batch) {
+  if (m < 0) m = 0;
   if (batch < 0) batch = 0;
-  return 256 + (size_t)rem_nnz * (size_t)batch * sizeof(float);
+  return 256 + (rem_nnz > 0 ? (size_t)m * (size_t)batch * sizeof(float2) : 0);
 }
 
 int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, const int32_t* pos,
@@ -712,43 +758,47 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
   SB_CHECK_ARG(blocks >= 0 && rem_nnz >= 0 && rem_nnz <= nnz && blocks * 256 + rem_nnz >= nnz &&
                blocks * kMinBlockEntries + rem_nnz <= nnz,
                "sparse_attention: block/remainder counts do not fit nnz");
-  const size_t need = sb_sparse_attention_scratch_bytes(rem_nnz, batch);
+  const size_t need = sb_sparse_attention_scratch_bytes(m, rem_nnz, batch);
   SB_CHECK_ARG(scratch && aligned16(scratch), "sparse_attention: scratch is null or misaligned");
   if (scratch_bytes < need)
     return fail(SB_ERR_WORKSPACE, "sparse_attention: scratch has %zu bytes, needs %zu", scratch_bytes, need);
   cudaStream_t st = (cudaStream_t)stream;
   AttnPlan p = attn_plan_view(const_cast<void*>(attn_plan), m, nnz);
   int* flags = static_cast<int*>(scratch);
-  float* rem = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
-  if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_SCORES)) {
-    // (columns from the plan's own copy; the entry list is only needed to find the mask values)
-    int rc = sddmm_remainder(m, d, rem_nnz, p.rem_pos, mask_val ? p.rem_ent : nullptr, p.rem_crd, mask_val, Q,
-                             ldq, K, ldk, rem, batch, stride_q, stride_k, rem_nnz, 1, st);
-    if (rc != SB_OK) return rc;
-  }
-  if (stages & SB_ATTN_STAGE_BLOCKS) {
-    if (mask_val && nnz > 0) {  // (without mask values the kernel never reads the flag)
+  AttnArgs a;
+  a.m = (int)m; a.RB = p.RB; a.rb_ptr = p.rb_ptr; a.blk_col = p.blk_col; a.blk_ent = p.blk_ent;
+  a.blk_mask = p.blk_mask; a.rem_pos = p.rem_pos; a.rem_ent = p.rem_ent; a.rem_crd = p.rem_crd;
+  a.mask_val = mask_val; a.mask_is_ones = flags;
+  a.Q = Q; a.K = K; a.V = V; a.O = O;
+  a.stats = reinterpret_cast<float2*>(static_cast<char*>(scratch) + 256);
+  a.has_rem = rem_nnz > 0 ? 1 : 0;
+  a.ldq = (unsigned)ldq; a.ldk = (unsigned)ldk; a.ldv = (unsigned)ldv; a.ldo = ldo;
+  a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
+  a.scale = scale;
+  if (stages & SB_ATTN_STAGE_SCATTERED) {
+    if (mask_val && nnz > 0) {  // (without mask values no kernel reads the flag)
       attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
       const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
       attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(mask_val, nnz, flags);
       SB_LAUNCH_CHECK("attn_mask_ones_kernel");
     }
-    AttnArgs a;
-    a.m = (int)m; a.RB = p.RB; a.rb_ptr = p.rb_ptr; a.blk_col = p.blk_col; a.blk_ent = p.blk_ent;
-    a.blk_mask = p.blk_mask; a.rem_pos = p.rem_pos; a.mask_val = mask_val; a.mask_is_ones = flags;
-    a.Q = Q; a.K = K; a.V = V; a.O = O; a.rem = rem;
-    a.ldq = (unsigned)ldq; a.ldk = (unsigned)ldk; a.ldv = (unsigned)ldv; a.ldo = ldo;
-    a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
-    a.stride_rem = rem_nnz;
-    a.scale = scale;
+    if (rem_nnz > 0) {
+      if (d == 32) {
+        dim3 grid((unsigned)ceil_div(ceil_div(m, 8), kScatWarps), (unsigned)batch);
+        attn_scattered_kernel<4><<<grid, kScatWarps * 32, 0, st>>>(a);
+      } else {
+        dim3 grid((unsigned)ceil_div(ceil_div(m, 4), kScatWarps), (unsigned)batch);
+        attn_scattered_kernel<8><<<grid, kScatWarps * 32, 0, st>>>(a);
+      }
+      SB_LAUNCH_CHECK("attn_scattered_kernel");
+    }
+  }
+  if (stages & SB_ATTN_STAGE_BLOCKS) {
     dim3 grid((unsigned)ceil_div(p.RB, kAttnWarps), (unsigned)batch);
     if (d == 32) attn_block_kernel<2><<<grid, kAttnWarps * 32, 0, st>>>(a);
     else attn_block_kernel<4><<<grid, kAttnWarps * 32, 0, st>>>(a);
     SB_LAUNCH_CHECK("attn_block_kernel");
   }
-  if (rem_nnz > 0 && (stages & SB_ATTN_STAGE_REMAINDER_PV))
-    return spmm_remainder(m, d, p.rem_pos, nullptr, p.rem_crd, rem, V, ldv, nullptr, 0, O, ldo, batch, rem_nnz,
-                          stride_v, stride_o, 1, st);
   return SB_OK;
 }
 

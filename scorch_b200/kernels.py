@@ -167,12 +167,12 @@ def _mask_is_all_ones(mask_val: torch.Tensor) -> bool:
 
 def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
                          attn_plan: Optional[AttnPlan] = None,
-                         out: Optional[torch.Tensor] = None, stages: int = 7) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, stages: int = 3) -> torch.Tensor:
     """O = softmax_rows(scale * mask_val .* (Q Kmat^T) on the stored entries) V in one call, the
     scores never written out.  Q: (m, d) or (batch, m, d); Kmat, V: (n, d) or (batch, n, d); head
     dimension d in FUSED_ATTENTION_D.  Rows without stored entries give zero rows.
-    ``stages``: 7 = the whole call; 1, 2, 4 = its three kernels one by one (in that order, same
-    arguments), for callers that time them."""
+    ``stages``: 3 = the whole call; 1, 2 = its two kernels one by one (scattered entries, then
+    blocks; same arguments and ``out``), for callers that time them."""
     pos = _dev(pos, torch.int32, "pos")
     crd = _dev(crd, torch.int32, "crd")
     m, nnz = pos.numel() - 1, crd.numel()
@@ -201,7 +201,7 @@ def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
     elif not (out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == shape and out.is_contiguous()):
         raise ValueError(f"out must be a contiguous float32 CUDA tensor of shape {shape}")
     L = _lib.lib()
-    sbytes = L.sb_sparse_attention_scratch_bytes(attn_plan.rem_nnz, batch)
+    sbytes = L.sb_sparse_attention_scratch_bytes(m, attn_plan.rem_nnz, batch)
     scratch = attn_plan.scratch(sbytes) if sbytes else None
     with torch.cuda.device(Q.device):
         check(L.sb_sparse_attention_csr_f32(m, n, d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val),

@@ -313,17 +313,21 @@ class _Gatherer:
                 self.comm = shard._buffers["comm_stream"] = torch.cuda.Stream(device=dev, priority=-1)
         self.main = torch.cuda.current_stream(dev) if self.on_gpu else None
 
-    def gather(self, name: str, send: torch.Tensor):
-        """Returns (gathered buffer, event or None)."""
+    def gather(self, name: str, send: torch.Tensor, produced=None):
+        """Returns (gathered buffer, event or None).  ``produced``: the event after which ``send``
+        holds its data (default: everything issued on the main stream so far)."""
         shard = self.shard
         if shard.world == 1:
+            if produced is not None:
+                self.main.wait_event(produced)
             return send, None
         buf = shard.buffer(name, (shard.world * send.shape[0], send.shape[1]), self.dev)
         if self.comm is None:
             dist.all_gather_into_tensor(buf, send, group=self.group)
             return buf, None
-        produced = torch.cuda.Event()
-        produced.record(self.main)
+        if produced is None:
+            produced = torch.cuda.Event()
+            produced.record(self.main)
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(produced)
             with _span(self.tl if self.on_gpu else None, "all_gather", self.comm):
@@ -347,16 +351,30 @@ def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x
     send = shard.buffer(name + "send", (shard.max_rows, k), dev)
     pending = []
     tlg = tl if dev.type == "cuda" else None
+    # optionally the dense transforms run on a stream of their own, beside the SpMM passes
+    side = None
+    if dev.type == "cuda" and shard.world > 1 and os.environ.get("SCORCH_B200_GCN_TRANSFORM_STREAM"):
+        side = shard._buffers.get("transform_stream")
+        if side is None:
+            side = shard._buffers["transform_stream"] = torch.cuda.Stream(device=dev)
+        ready = torch.cuda.Event()
+        ready.record(g.main)          # the layer's input and the send buffer are free from here on
+        side.wait_event(ready)
 
     def produce(c):
         lo, hi = min(split.offsets[c], shard.rows), min(split.offsets[c + 1], shard.rows)
-        if hi > lo:
-            with _span(tlg, "dense_transform"):
-                if weight is not None:
-                    torch.matmul(x_local[lo:hi], weight, out=send[lo:hi])
-                else:
-                    send[lo:hi].copy_(x_local[lo:hi])
-        pending.append(g.gather(f"{name}recv{c}", send[split.offsets[c]:split.offsets[c + 1]]))
+        produced = None
+        with torch.cuda.stream(side) if side is not None else _span(None, ""):
+            if hi > lo:
+                with _span(tlg, "dense_transform", side):
+                    if weight is not None:
+                        torch.matmul(x_local[lo:hi], weight, out=send[lo:hi])
+                    else:
+                        send[lo:hi].copy_(x_local[lo:hi])
+            if side is not None:
+                produced = torch.cuda.Event()
+                produced.record(side)
+        pending.append(g.gather(f"{name}recv{c}", send[split.offsets[c]:split.offsets[c + 1]], produced))
 
     def consume(c):
         buf, ev = pending[c]

@@ -115,7 +115,7 @@ def test_sparse_attention_stages_equal_whole_call():
     ap = K.AttnPlan(pos, crd)
     whole = K.sparse_attention_csr(pos, crd, mv, dev(Q), dev(Km), dev(V), scale=0.125, attn_plan=ap)
     out = torch.full_like(whole, float("nan"))
-    for stage in (1, 2, 4):
+    for stage in (1, 2):
         K.sparse_attention_csr(pos, crd, mv, dev(Q), dev(Km), dev(V), scale=0.125, attn_plan=ap, out=out,
                                stages=stage)
     assert torch.equal(whole, out)
