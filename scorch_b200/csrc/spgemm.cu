@@ -274,8 +274,56 @@ struct CsrIn {
   const double* row_scale;   // numeric phase, float types: fixed-point scale per output row
 };
 
-// One warp per row (bins 0, 1).  The warp's 4 groups of 8 lanes take alternate entries of the A
-// row; a group's lanes span the B row (B rows are short on average).
+// The products of A entries [pa0, pa1) (at most 32, one per lane) spread evenly over the lanes
+// of a warp: lane l looks up the B row of entry pa0 + l, a warp scan of the row lengths numbers
+// the products, and every lane then takes products lane, lane + 32, ... — a 5-step search over
+// the scanned lengths tells which entry a product belongs to.  No lane idles on a short B row and
+// the index loads of 32 entries are in flight together, instead of one dependent chain
+// (A entry -> B row pointers -> B entries) per entry.  `emit(a_value, pb)` is called once per
+// product with the value of its A entry (T(0) in the symbolic phase) and its position in B.
+template <typename T, bool NUMERIC, typename F>
+__device__ __forceinline__ void expand_products(const CsrIn& in, int pa0, int pa1, int lane, F&& emit) {
+  const int pa = pa0 + lane;
+  int bb = 0, len = 0;
+  T a = T(0);
+  if (pa < pa1) {
+    const int j = __ldg(in.Acrd + pa);
+    bb = __ldg(in.Bpos + j);
+    len = __ldg(in.Bpos + j + 1) - bb;
+    if (NUMERIC) a = static_cast<const T*>(in.Aval)[pa];
+  }
+  int incl = len;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(FULL, incl, o);
+    if (lane >= o) incl += y;
+  }
+  const int total = __shfl_sync(FULL, incl, 31);
+  const int excl = incl - len;
+  for (int q0 = 0; q0 < total; q0 += 32) {
+    const int q = q0 + lane;
+    // largest e with excl[e] <= q (lanes past the end search too: shuffles need the whole warp)
+    int e = 0;
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) {
+      const int v = __shfl_sync(FULL, excl, e + step);
+      if (v <= q) e += step;
+    }
+    const int e_excl = __shfl_sync(FULL, excl, e);
+    const int e_bb = __shfl_sync(FULL, bb, e);
+    T e_a;
+    if constexpr (sizeof(T) == 8) {
+      const long long bits = __shfl_sync(FULL, *reinterpret_cast<const long long*>(&a), e);
+      memcpy(&e_a, &bits, 8);
+    } else {
+      const int bits = __shfl_sync(FULL, *reinterpret_cast<const int*>(&a), e);
+      memcpy(&e_a, &bits, 4);
+    }
+    if (q < total) emit(e_a, e_bb + (q - e_excl));
+  }
+}
+
+// One warp per row (bins 0, 1): 32 A entries at a time, their products spread over the lanes.
 template <typename T, int S, bool NUMERIC>
 __global__ void __launch_bounds__(128)
 spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
@@ -296,21 +344,15 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
   double scale = 1.0;
   if (NUMERIC && IsFloat<T>::value) scale = in.row_scale[i];
   const bool fixed = scale == scale;
-  const T* Aval = static_cast<const T*>(in.Aval);
   const T* Bval = static_cast<const T*>(in.Bval);
-  const int g = lane >> 3, l = lane & 7;
   const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
   int fresh = 0;
-  for (int pa = ab + g; pa < ae; pa += 4) {
-    const int j = __ldg(in.Acrd + pa);
-    T a = T(0);
-    if (NUMERIC) a = Aval[pa];
-    const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
-    for (int pb = bb + l; pb < be; pb += 8) {
+  for (int pa0 = ab; pa0 < ae; pa0 += 32) {
+    expand_products<T, NUMERIC>(in, pa0, min(ae, pa0 + 32), lane, [&](T a, int pb) {
       const int c = __ldg(in.Bcrd + pb);
       const int h = hash_find_or_insert<S>(keys, c, fresh);
       if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
-    }
+    });
   }
   __syncwarp();
   if (!NUMERIC) {
@@ -329,7 +371,7 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
   }
 }
 
-// One CTA per row (bins 2, 3): warps take alternate entries of the A row, lanes span the B row.
+// One CTA per row (bins 2-4): warps take alternate slabs of 32 entries of the A row.
 template <typename T, int S, int NT, bool NUMERIC>
 __global__ void __launch_bounds__(NT)
 spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __restrict__ row_cnt,
@@ -352,20 +394,16 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
   double scale = 1.0;
   if (NUMERIC && IsFloat<T>::value) scale = in.row_scale[i];
   const bool fixed = scale == scale;
-  const T* Aval = static_cast<const T*>(in.Aval);
   const T* Bval = static_cast<const T*>(in.Bval);
   const int ab = __ldg(in.Apos + i), ae = __ldg(in.Apos + i + 1);
   int fresh = 0;
-  for (int pa = ab + warp; pa < ae; pa += NT / 32) {
-    const int j = __ldg(in.Acrd + pa);
-    T a = T(0);
-    if (NUMERIC) a = Aval[pa];
-    const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
-    for (int pb = bb + lane; pb < be; pb += 32) {
+  // warps take slabs of 32 A entries; a slab's products are spread over the warp's lanes
+  for (int pa0 = ab + 32 * warp; pa0 < ae; pa0 += NT) {
+    expand_products<T, NUMERIC>(in, pa0, min(ae, pa0 + 32), lane, [&](T a, int pb) {
       const int c = __ldg(in.Bcrd + pb);
       const int h = hash_find_or_insert<S>(keys, c, fresh);
       if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
-    }
+    });
   }
   if (!NUMERIC) {
 #pragma unroll
@@ -386,7 +424,7 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
   }
 }
 
-// Bin 4 (rows whose products do not fit a shared-memory table): dense bitmap (+ accumulator) of
+// Bin 5 (rows whose products do not fit a shared-memory table): dense bitmap (+ accumulator) of
 // n columns per row in the workspace.  Rows are handled in batches of up to `slots` rows, one
 // slot each; a row's A entries are cut into chunks of kDenseChunk entries and the (row, chunk)
 // tasks of a batch are handed out through an atomic queue, so a hub row with hundreds of
@@ -394,8 +432,6 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
 // (a counter per row, no spinning) walks the row's bitmap in ascending column order, emits the
 // row and leaves bitmap and accumulator all-zero for the next batch.
 constexpr int kDenseChunk = 2048;     // A entries per task
-constexpr int kLongBRow = 4096;       // B rows at least this long are handled by the whole CTA
-constexpr int kDeferCap = 32;
 
 struct DenseCtl {
   int* task_pref;  // [slots + 1]
@@ -420,18 +456,6 @@ __global__ void dense_batch_setup_kernel(const int* __restrict__ rows, int r0, i
 }
 
 template <typename T, bool NUMERIC>
-__device__ __forceinline__ void dense_add_brow(const CsrIn& in, int j, T a, unsigned* bitmap, Slot* acc,
-                                               int start, int stride, double scale, bool fixed) {
-  const T* Bval = static_cast<const T*>(in.Bval);
-  const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
-  for (int pb = bb + start; pb < be; pb += stride) {
-    const int c = __ldg(in.Bcrd + pb);
-    if (NUMERIC) acc_add<T>(acc + c, a, Bval[pb], scale, fixed);
-    atomicOr(&bitmap[c >> 5], 1u << (c & 31));
-  }
-}
-
-template <typename T, bool NUMERIC>
 __global__ void __launch_bounds__(256)
 spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long long words,
                     unsigned* __restrict__ bitmap_all, Slot* __restrict__ acc_all, long long n,
@@ -441,16 +465,11 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
   __shared__ int s_base;
   __shared__ int s_task;
   __shared__ int s_last;
-  __shared__ int s_ndefer;
-  __shared__ int s_defer[kDeferCap];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const T* Aval = static_cast<const T*>(in.Aval);
   const int total = __ldg(ctl.task_pref + nb);
   while (true) {
-    if (tid == 0) {
-      s_task = atomicAdd(ctl.queue, 1);
-      s_ndefer = 0;
-    }
+    if (tid == 0) s_task = atomicAdd(ctl.queue, 1);
     __syncthreads();
     const int task = s_task;
     if (task >= total) return;
@@ -471,28 +490,14 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
     const bool fixed = scale == scale;
     const int ab = __ldg(in.Apos + i) + chunk * kDenseChunk;
     const int ae = min(__ldg(in.Apos + i + 1), ab + kDenseChunk);
-    // warps take A entries; long B rows are put aside for the whole CTA
-    for (int pa = ab + warp; pa < ae; pa += 8) {
-      const int j = __ldg(in.Acrd + pa);
-      const int blen = __ldg(in.Bpos + j + 1) - __ldg(in.Bpos + j);
-      bool mine = true;
-      if (blen >= kLongBRow) {
-        int slot = 0;
-        if (lane == 0) slot = atomicAdd(&s_ndefer, 1);
-        slot = __shfl_sync(FULL, slot, 0);
-        if (slot < kDeferCap) {
-          if (lane == 0) s_defer[slot] = pa;
-          mine = false;
-        }
-      }
-      if (mine) dense_add_brow<T, NUMERIC>(in, j, NUMERIC ? Aval[pa] : T(0), bitmap, acc, lane, 32, scale, fixed);
-    }
-    __syncthreads();
-    const int nd = min(s_ndefer, kDeferCap);
-    for (int q = 0; q < nd; q++) {
-      const int pa = s_defer[q];
-      dense_add_brow<T, NUMERIC>(in, __ldg(in.Acrd + pa), NUMERIC ? Aval[pa] : T(0), bitmap, acc, tid, 256,
-                                 scale, fixed);
+    // warps take slabs of 32 A entries; a slab's products are spread over the warp's lanes (a hub
+    // row of B is shared by all lanes like any other)
+    for (int pa0 = ab + 32 * warp; pa0 < ae; pa0 += 256) {
+      expand_products<T, NUMERIC>(in, pa0, min(ae, pa0 + 32), lane, [&](T av, int pb) {
+        const int c = __ldg(in.Bcrd + pb);
+        if (NUMERIC) acc_add<T>(acc + c, av, static_cast<const T*>(in.Bval)[pb], scale, fixed);
+        atomicOr(&bitmap[c >> 5], 1u << (c & 31));
+      });
     }
     // publish this chunk, then find out whether it was the row's last one
     __threadfence();
