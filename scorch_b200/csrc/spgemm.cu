@@ -281,8 +281,11 @@ struct CsrIn {
 // the index loads of 32 entries are in flight together, instead of one dependent chain
 // (A entry -> B row pointers -> B entries) per entry.  `emit(a_value, pb)` is called once per
 // product with the value of its A entry (T(0) in the symbolic phase) and its position in B.
-template <typename T, bool NUMERIC, typename F>
-__device__ __forceinline__ void expand_products(const CsrIn& in, int pa0, int pa1, int lane, F&& emit) {
+// `defer(pa, len)` may take an entry out of the warp's share (it returns true and deals with the
+// entry's products itself): the dense rows hand B rows of hub length to the whole CTA that way.
+template <typename T, bool NUMERIC, typename F, typename D>
+__device__ __forceinline__ void expand_products(const CsrIn& in, int pa0, int pa1, int lane, F&& emit,
+                                                D&& defer) {
   const int pa = pa0 + lane;
   int bb = 0, len = 0;
   T a = T(0);
@@ -290,6 +293,7 @@ __device__ __forceinline__ void expand_products(const CsrIn& in, int pa0, int pa
     const int j = __ldg(in.Acrd + pa);
     bb = __ldg(in.Bpos + j);
     len = __ldg(in.Bpos + j + 1) - bb;
+    if (defer(pa, len)) len = 0;
     if (NUMERIC) a = static_cast<const T*>(in.Aval)[pa];
   }
   int incl = len;
@@ -352,7 +356,7 @@ spgemm_warp_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __res
       const int c = __ldg(in.Bcrd + pb);
       const int h = hash_find_or_insert<S>(keys, c, fresh);
       if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
-    });
+    }, [](int, int) { return false; });
   }
   __syncwarp();
   if (!NUMERIC) {
@@ -403,7 +407,7 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
       const int c = __ldg(in.Bcrd + pb);
       const int h = hash_find_or_insert<S>(keys, c, fresh);
       if (NUMERIC) acc_add<T>(vals + h, a, Bval[pb], scale, fixed);
-    });
+    }, [](int, int) { return false; });
   }
   if (!NUMERIC) {
 #pragma unroll
@@ -432,6 +436,8 @@ spgemm_cta_kernel(const int* __restrict__ rows, int nrows, CsrIn in, int* __rest
 // (a counter per row, no spinning) walks the row's bitmap in ascending column order, emits the
 // row and leaves bitmap and accumulator all-zero for the next batch.
 constexpr int kDenseChunk = 2048;     // A entries per task
+constexpr int kLongBRow = 2048;       // B rows at least this long are walked by the whole CTA
+constexpr int kDeferCap = 64;
 
 struct DenseCtl {
   int* task_pref;  // [slots + 1]
@@ -465,11 +471,15 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
   __shared__ int s_base;
   __shared__ int s_task;
   __shared__ int s_last;
+  __shared__ int s_ndefer;
+  __shared__ int s_defer[kDeferCap];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const T* Aval = static_cast<const T*>(in.Aval);
   const int total = __ldg(ctl.task_pref + nb);
   while (true) {
-    if (tid == 0) s_task = atomicAdd(ctl.queue, 1);
+    if (tid == 0) {
+      s_task = atomicAdd(ctl.queue, 1);
+      s_ndefer = 0;
+    }
     __syncthreads();
     const int task = s_task;
     if (task >= total) return;
@@ -490,14 +500,30 @@ spgemm_dense_kernel(const int* __restrict__ rows, int r0, int nb, CsrIn in, long
     const bool fixed = scale == scale;
     const int ab = __ldg(in.Apos + i) + chunk * kDenseChunk;
     const int ae = min(__ldg(in.Apos + i + 1), ab + kDenseChunk);
-    // warps take slabs of 32 A entries; a slab's products are spread over the warp's lanes (a hub
-    // row of B is shared by all lanes like any other)
+    // warps take slabs of 32 A entries; a slab's products are spread over the warp's lanes.  B
+    // rows of hub length are put aside and walked by the whole CTA afterwards.
+    auto add = [&](T av, int pb) {
+      const int c = __ldg(in.Bcrd + pb);
+      if (NUMERIC) acc_add<T>(acc + c, av, static_cast<const T*>(in.Bval)[pb], scale, fixed);
+      atomicOr(&bitmap[c >> 5], 1u << (c & 31));
+    };
     for (int pa0 = ab + 32 * warp; pa0 < ae; pa0 += 256) {
-      expand_products<T, NUMERIC>(in, pa0, min(ae, pa0 + 32), lane, [&](T av, int pb) {
-        const int c = __ldg(in.Bcrd + pb);
-        if (NUMERIC) acc_add<T>(acc + c, av, static_cast<const T*>(in.Bval)[pb], scale, fixed);
-        atomicOr(&bitmap[c >> 5], 1u << (c & 31));
+      expand_products<T, NUMERIC>(in, pa0, min(ae, pa0 + 32), lane, add, [&](int pa, int len) {
+        if (len < kLongBRow) return false;
+        const int slot = atomicAdd(&s_ndefer, 1);
+        if (slot >= kDeferCap) return false;
+        s_defer[slot] = pa;
+        return true;
       });
+    }
+    __syncthreads();
+    const int nd = min(s_ndefer, kDeferCap);
+    for (int q = 0; q < nd; q++) {
+      const int pa = s_defer[q];
+      const int j = __ldg(in.Acrd + pa);
+      const T av = NUMERIC ? static_cast<const T*>(in.Aval)[pa] : T(0);
+      const int bb = __ldg(in.Bpos + j), be = __ldg(in.Bpos + j + 1);
+      for (int pb = bb + tid; pb < be; pb += 256) add(av, pb);
     }
     // publish this chunk, then find out whether it was the row's last one
     __threadfence();

@@ -19,13 +19,16 @@
 #define SB_SPMM_INFLIGHT 32
 #endif
 
-// mean stored entries per row below which a launch takes several rows per warp: 64 where one
-// column tile covers the operand (k <= 256), 24 for wider operands taken in column panels
+// mean stored entries per row below which a launch takes several rows per warp: 64 where the
+// whole warp spans one column tile that covers the operand (128 < k <= 256: four rows per warp
+// one after the other), 24 otherwise (narrow tiles, a row per lane group: a 4096-row, 41-per-row,
+// 64-column product measured 16 us that way against 10 us with a warp per row; and wide operands
+// taken in column panels)
 #ifndef SB_SPMM_SHORT_ROW_MEAN
-#define SB_SPMM_SHORT_ROW_MEAN 64
+#define SB_SPMM_SHORT_ROW_MEAN 24
 #endif
-#ifndef SB_SPMM_SHORT_ROW_MEAN_WIDE
-#define SB_SPMM_SHORT_ROW_MEAN_WIDE 24
+#ifndef SB_SPMM_SHORT_ROW_MEAN_FULL_WARP
+#define SB_SPMM_SHORT_ROW_MEAN_FULL_WARP 64
 #endif
 
 namespace sb {
@@ -775,7 +778,8 @@ static int spmm_csr_f32_impl(int64_t m, int64_t n, int64_t k, int64_t nnz, const
   a.val_compact = 0;
   a.accumulate = accumulate ? 1 : 0;
   // many short rows (e.g. one row chunk's share of a matrix): several rows per warp
-  a.short_rows = (nnz < (int64_t)(k <= 256 ? SB_SPMM_SHORT_ROW_MEAN : SB_SPMM_SHORT_ROW_MEAN_WIDE) * m) ? 1 : 0;
+  a.short_rows = (nnz < (int64_t)((k > 128 && k <= 256) ? SB_SPMM_SHORT_ROW_MEAN_FULL_WARP
+                                                        : SB_SPMM_SHORT_ROW_MEAN) * m) ? 1 : 0;
   return spmm_vec_dispatch(a, k, ldb, ldc, stride_b, stride_c, B, C, batch, plan, nnz, plan_segments, scratch, st);
 }
 
