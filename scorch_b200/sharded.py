@@ -92,15 +92,21 @@ def row_block(pos: torch.Tensor, crd: torch.Tensor, val: torch.Tensor, rank: int
 
 def default_chunks(world: int):
     """(first layer, second layer) row chunks of a GCN: one piece with one rank (nothing to
-    overlap); otherwise the 256-wide first layer in five pieces of 1/8, 1/8, 1/4, 1/4, 1/4 of the
-    rows and the 64-wide second one in eight equal pieces.  SCORCH_B200_GCN_CHUNKS overrides:
-    "6" (both layers), "4;8" (first; second), or proportions such as "1,1,2,2,2;8"."""
+    overlap).  Otherwise the first piece is an eighth of the rows, so that the first gather is
+    short, and the 256-wide first layer goes in pieces of 1/8, 3/8, 1/2 up to four ranks (every
+    extra pass cost 0.3-0.4 ms at four ranks, and the gathers are short against the passes) and of
+    1/8, 1/8, 1/4, 1/4, 1/4 beyond (gather and pass take about as long there, so finer pieces
+    overlap better); the 64-wide second layer goes in eight equal pieces.
+    SCORCH_B200_GCN_CHUNKS overrides: "6" (both layers), "4;8" (first; second), or proportions
+    such as "1,1,2,2,2;8"."""
     env = os.environ.get("SCORCH_B200_GCN_CHUNKS")
     if env:
         parts = [[int(x) for x in p.split(",")] for p in env.split(";")]
         parts = [p[0] if len(p) == 1 else p for p in parts]
         return parts[0], parts[-1]
-    return (1, 1) if world == 1 else ([1, 1, 2, 2, 2], 8)
+    if world == 1:
+        return 1, 1
+    return ([1, 3, 4] if world <= 4 else [1, 1, 2, 2, 2]), 8
 
 
 def chunk_offsets(rows: int, spec) -> List[int]:
@@ -351,9 +357,10 @@ def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x
     send = shard.buffer(name + "send", (shard.max_rows, k), dev)
     pending = []
     tlg = tl if dev.type == "cuda" else None
-    # optionally the dense transforms run on a stream of their own, beside the SpMM passes
+    # the dense transforms run on a stream of their own, beside the SpMM passes (0.6 ms of 11.9 at
+    # four ranks); SCORCH_B200_GCN_TRANSFORM_STREAM=0 puts them back on the main stream
     side = None
-    if dev.type == "cuda" and shard.world > 1 and os.environ.get("SCORCH_B200_GCN_TRANSFORM_STREAM"):
+    if dev.type == "cuda" and shard.world > 1 and os.environ.get("SCORCH_B200_GCN_TRANSFORM_STREAM", "1") != "0":
         side = shard._buffers.get("transform_stream")
         if side is None:
             side = shard._buffers["transform_stream"] = torch.cuda.Stream(device=dev)
