@@ -227,8 +227,9 @@ class SparseAttention(Workload):
         self.attn_plan = (None if no_blocks or os.environ.get("SCORCH_B200_NO_FUSED")
                           else P.attention_plan(self.pos, self.crd, self.d, self.d))
         self.block_plan = None if no_blocks or self.attn_plan else P.attention_block_plan(self.pos, self.crd)
+        self.band = isinstance(self.attn_plan, K.AttnBandPlan)
         if self.attn_plan:
-            self.kernels = ("attn_scattered_kernel", "attn_block_kernel")
+            self.kernels = ("attn_scattered_kernel", "attn_band_kernel" if self.band else "attn_block_kernel")
         else:
             self.kernels = ("sddmm_kernel", "csr_row_softmax_kernel", "spmm_rows_kernel")
         self.scores = (None if self.attn_plan else
@@ -248,6 +249,11 @@ class SparseAttention(Workload):
 
     def run_info(self):
         bp = self.attn_plan or self.block_plan
+        if self.band:
+            return {"units_this_rank": self.units,
+                    "path": "one attention call: scattered entries by the gather kernel, 128-row tiles x "
+                            "384-column windows on tcgen05 (S, P and O in tensor memory; scores not stored)",
+                    "entries_inside_windows": bp.inside, "entries_outside_windows": bp.rem_nnz}
         return {"units_this_rank": self.units,
                 "path": ("one attention call (scattered entries and blocks share a running softmax; scores not stored)"
                          if self.attn_plan else "sddmm, row softmax, spmm"),
@@ -258,6 +264,15 @@ class SparseAttention(Workload):
         """Algorithmic bytes per launch (each array read once / written once)."""
         nnz, s, d, u = self.nnz, self.seq, self.d, self.units
         idx = (s + 1) * 4 + nnz * 4
+        if self.band:
+            rem = self.attn_plan.rem_nnz
+            rem_idx = (s + 1) * 4 + 2 * rem * 4
+            return {
+                "attn_scattered_kernel": rem_idx + rem * 4 + u * (4 * s * d * 4 + s * 8),
+                # tiles: 12 mask words and the first entry per row, mask values of the window entries,
+                # Q, K, V, unnormalised O and (maximum, sum) in, O out
+                "attn_band_kernel": s * 13 * 4 + (nnz - rem) * 4 + u * (5 * s * d * 4 + s * 8),
+            }
         if self.attn_plan:
             rem, blocks = self.attn_plan.rem_nnz, self.attn_plan.blocks
             rem_idx = (s + 1) * 4 + 2 * rem * 4          # rem_pos, rem_ent, crd of the listed entries
@@ -319,7 +334,7 @@ class SparseAttention(Workload):
         return self.host_out.numel() * 4
 
     def traffic_key(self):
-        return self.name + (":one_call" if self.attn_plan else ":three_operators")
+        return self.name + ((":one_call_band" if self.band else ":one_call") if self.attn_plan else ":three_operators")
 
     # -- CPU reference on a bounded sample ---------------------------------------------------------
     def cpu_sample(self, units: int, repeats: int):

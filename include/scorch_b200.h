@@ -286,6 +286,51 @@ SB_API int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t 
                                        int stages, void* stream);
 
 /* --------------------------------------------------------------------------------------------
+ * The same sparse attention for banded masks on the tcgen05 tensor cores (head dimension 64).
+ * Replaces: the same operator sequence (bench/bench_sparse_transformer.py:304-382).
+ * A band plan cuts the mask rows into tiles of SB_ATTN_BAND_ROWS rows and gives tile t the window
+ * of SB_ATTN_BAND_COLS columns that starts at clamp(t * ROWS - (COLS - ROWS) / 2, 0, n - COLS);
+ * per row it holds the stored columns inside the window as bits and the index of the row's first
+ * entry there; entries outside the windows go to a CSR remainder list (the scattered entries).
+ * Columns must be ascending and unique per row (the reference's CSR).
+ *   sb_attn_band_plan_build : synchronises; *inside_host = entries inside the windows,
+ *                          *rem_nnz_host = entries outside (inside + outside = nnz).  Worth using
+ *                          when most entries are inside; any mask gives correct results.
+ *   sb_sparse_attention_band_f32 : same arguments, alignment rules, scratch and stages as
+ *                          sb_sparse_attention_csr_f32; the scattered entries first (the same
+ *                          gather kernel), then one CTA per (tile, batch item): S = Q K^T and
+ *                          O += P V as tcgen05.mma kind::tf32 with the TF32x3 split, S, P and O in
+ *                          tensor memory.  Every wait on the tensor cores is bounded; when one runs
+ *                          out the CTA gives up and sb_attn_band_status (synchronises the device)
+ *                          returns non-zero afterwards, else 0.
+ *   sb_attn_band_probe   : self-test of the tensor-core path on one tile with every window column
+ *                          counted as stored and scale 1: `raw_scores` receives the 128 x 384
+ *                          products Q K^T; `tmem_image` (may be null) the tile's 128 x 512
+ *                          tensor-memory cells at the end: columns [0,384) the hi parts of
+ *                          P = exp2(log2(e) S - row max), [384,448) the unnormalised O = P V,
+ *                          [448,512) the lo parts of P's last 64 columns.  O is not written.
+ * -------------------------------------------------------------------------------------------- */
+#define SB_ATTN_BAND_ROWS 128
+#define SB_ATTN_BAND_COLS 384
+SB_API size_t sb_attn_band_plan_bytes(int64_t m, int64_t nnz);
+SB_API int sb_attn_band_plan_build(int64_t m, int64_t n, int64_t nnz, const int32_t* pos,
+                                   const int32_t* crd, void* plan, size_t plan_bytes,
+                                   int64_t* inside_host, int64_t* rem_nnz_host, void* stream);
+SB_API int sb_sparse_attention_band_f32(int64_t m, int64_t n, int64_t d, int64_t nnz,
+                                        const int32_t* pos, const int32_t* crd,
+                                        const float* mask_val, const float* Q, int64_t ldq,
+                                        const float* K, int64_t ldk, const float* V, int64_t ldv,
+                                        float scale, float* O, int64_t ldo, int64_t batch,
+                                        int64_t stride_q, int64_t stride_k, int64_t stride_v,
+                                        int64_t stride_o, const void* band_plan, int64_t rem_nnz,
+                                        void* scratch, size_t scratch_bytes, int stages,
+                                        void* stream);
+SB_API int sb_attn_band_probe(int64_t m, int64_t n, int64_t d, int64_t tile, const float* Q,
+                              int64_t ldq, const float* K, int64_t ldk, const float* V, int64_t ldv,
+                              float* raw_scores, float* tmem_image, void* stream);
+SB_API int sb_attn_band_status(void);
+
+/* --------------------------------------------------------------------------------------------
  * CSR x CSR SpGEMM (Gustavson), two phases.  Output rows have strictly ascending, unique
  * columns; the structure is the symbolic union (entries whose products cancel are kept).
  * Replaces: spmspm_csr<T> csrc/kernels.h:51-202 (prebuilt_spmspm_csr_{f32,f64,i32,i64},

@@ -23,6 +23,7 @@
 
 #include <algorithm>
 
+#include "attention.cuh"
 #include "common.cuh"
 #include "mma_tf32.cuh"
 
@@ -223,57 +224,6 @@ __global__ void attn_mask_ones_kernel(const float* __restrict__ mask_val, long l
   if (!__all_sync(FULL, ones) && (threadIdx.x & 31) == 0) *flag = 0;
 }
 __global__ void attn_flag_init_kernel(int* flag) { *flag = 1; }
-
-// ---- the block kernel ---------------------------------------------------------------------------------
-struct AttnArgs {
-  int m;
-  int RB;
-  const int* rb_ptr;
-  const int* blk_col;
-  const int* blk_ent;
-  const int* blk_mask;
-  const int* rem_pos;
-  const float* mask_val;  // may be null
-  const int* mask_is_ones; // device flag: every mask value is 1.0f (the mask values are then not read)
-  const float* Q;
-  const float* K;
-  const float* V;
-  float* O;
-  float2* stats;          // [batch][m]: (running maximum in log2 units, sum) of each row's scattered entries
-  int has_rem;            // the scattered-entry kernel ran: O and stats hold its results
-  const int* rem_ent;     // entry index in the mask of each scattered entry (for its mask value)
-  const int* rem_crd;     // its column
-  unsigned ldq, ldk, ldv;
-  long long ldo;
-  long long stride_q, stride_k, stride_v, stride_o;
-  float scale;
-};
-
-// x = hi + lo with both parts valid TF32 values (low 13 mantissa bits zero): hi is x truncated,
-// lo the truncated remainder, so hi*hi + hi*lo + lo*hi misses the product by ~2^-20 relative.
-// (Two logic operations and one subtraction; rounding instead of truncating measured slower
-// and no more accurate at the fp32 level.)
-__device__ __forceinline__ void attn_split(float x, unsigned& hi, unsigned& lo) {
-  hi = __float_as_uint(x) & 0xffffe000u;
-  lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
-}
-// 2^x on the special-function unit (ex2.approx: 2 ulp; 2^-inf = 0)
-__device__ __forceinline__ float attn_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// 256-bit read-only load (32-byte aligned): one instruction covers whole 128-byte lines of the
-// K / V rows, half the L1 wavefronts of 128-bit loads
-struct Float8 { float v[8]; };
-__device__ __forceinline__ Float8 ldg8(const float* p) {
-  Float8 r;
-  asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]),
-                 "=f"(r.v[6]), "=f"(r.v[7])
-               : "l"(p));
-  return r;
-}
 
 // ---- the scattered entries -----------------------------------------------------------------------
 // L = d / 8 lanes per mask row (a lane holds 8 features of the row's Q and 8 columns of its
@@ -667,6 +617,32 @@ attn_block_kernel(AttnArgs a) {
 
 }  // namespace sb
 
+namespace sb {
+
+int attn_launch_scattered(const AttnArgs& a, int64_t d, int64_t nnz, int64_t rem_nnz, int64_t batch,
+                          int* flags, cudaStream_t st) {
+  const int64_t m = a.m;
+  if (a.mask_val && nnz > 0) {  // (without mask values no kernel reads the flag)
+    attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
+    const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
+    attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(a.mask_val, nnz, flags);
+    SB_LAUNCH_CHECK("attn_mask_ones_kernel");
+  }
+  if (rem_nnz > 0) {
+    if (d == 32) {
+      dim3 grid((unsigned)ceil_div(ceil_div(m, 8), kScatWarps), (unsigned)batch);
+      attn_scattered_kernel<4><<<grid, kScatWarps * 32, 0, st>>>(a);
+    } else {
+      dim3 grid((unsigned)ceil_div(ceil_div(m, 4), kScatWarps), (unsigned)batch);
+      attn_scattered_kernel<8><<<grid, kScatWarps * 32, 0, st>>>(a);
+    }
+    SB_LAUNCH_CHECK("attn_scattered_kernel");
+  }
+  return SB_OK;
+}
+
+}  // namespace sb
+
 using namespace sb;
 
 extern "C" {
@@ -776,22 +752,8 @@ int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, co
   a.stride_q = stride_q; a.stride_k = stride_k; a.stride_v = stride_v; a.stride_o = stride_o;
   a.scale = scale;
   if (stages & SB_ATTN_STAGE_SCATTERED) {
-    if (mask_val && nnz > 0) {  // (without mask values no kernel reads the flag)
-      attn_flag_init_kernel<<<1, 1, 0, st>>>(flags);
-      const unsigned blocks_ones = (unsigned)std::min<int64_t>(ceil_div(nnz, 256 * 8), 4 * sm_count());
-      attn_mask_ones_kernel<<<blocks_ones, 256, 0, st>>>(mask_val, nnz, flags);
-      SB_LAUNCH_CHECK("attn_mask_ones_kernel");
-    }
-    if (rem_nnz > 0) {
-      if (d == 32) {
-        dim3 grid((unsigned)ceil_div(ceil_div(m, 8), kScatWarps), (unsigned)batch);
-        attn_scattered_kernel<4><<<grid, kScatWarps * 32, 0, st>>>(a);
-      } else {
-        dim3 grid((unsigned)ceil_div(ceil_div(m, 4), kScatWarps), (unsigned)batch);
-        attn_scattered_kernel<8><<<grid, kScatWarps * 32, 0, st>>>(a);
-      }
-      SB_LAUNCH_CHECK("attn_scattered_kernel");
-    }
+    const int rc = attn_launch_scattered(a, d, nnz, rem_nnz, batch, flags, st);
+    if (rc != SB_OK) return rc;
   }
   if (stages & SB_ATTN_STAGE_BLOCKS) {
     dim3 grid((unsigned)ceil_div(p.RB, kAttnWarps), (unsigned)batch);

@@ -7,7 +7,7 @@ path lives in ``scorch_ops``).
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
+from typing import Optional, Tuple, Union
 
 import torch
 
@@ -150,6 +150,79 @@ def attn_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> AttnPlan:
     return plan
 
 
+class AttnBandPlan:
+    """Band plan of one CSR attention mask for the tcgen05 path: per 128-row tile a window of 384
+    columns around the diagonal, the stored columns inside it as bits per row, and a CSR list of
+    the entries outside; see include/scorch_b200.h.  ``inside_fraction`` is the share of the
+    stored entries that lie inside the windows."""
+
+    ROWS, COLS = 128, 384
+
+    def __init__(self, pos: torch.Tensor, crd: torch.Tensor, n: Optional[int] = None):
+        pos, crd = _dev(pos, torch.int32, "pos"), _dev(crd, torch.int32, "crd")
+        self.m, self.nnz = pos.numel() - 1, crd.numel()
+        self.n = self.m if n is None else n
+        L = _lib.lib()
+        nbytes = L.sb_attn_band_plan_bytes(self.m, self.nnz)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=pos.device)
+        a, r = C.c_int64(0), C.c_int64(0)
+        with torch.cuda.device(pos.device):
+            check(L.sb_attn_band_plan_build(self.m, self.n, self.nnz, pos.data_ptr(), crd.data_ptr(),
+                                            self.buf.data_ptr(), nbytes, C.byref(a), C.byref(r), _stream()))
+        self.inside, self.rem_nnz = int(a.value), int(r.value)
+        self._scratch: Optional[torch.Tensor] = None
+
+    @property
+    def inside_fraction(self) -> float:
+        return self.inside / self.nnz if self.nnz else 0.0
+
+    @property
+    def window_fill(self) -> float:
+        """Stored entries inside the windows / window cells (rows x 384)."""
+        return self.inside / (self.m * self.COLS) if self.m else 0.0
+
+    def window_start(self, tile: int) -> int:
+        return max(0, min(tile * self.ROWS - (self.COLS - self.ROWS) // 2, self.n - self.COLS))
+
+    scratch = AttnPlan.scratch
+
+
+def attn_band_plan_for(pos: torch.Tensor, crd: torch.Tensor) -> AttnBandPlan:
+    """Band plan of a square mask, cached on the ``crd`` tensor object (rebuilt after in-place
+    writes)."""
+    cached = getattr(crd, "_sb_attn_band_plan", None)
+    if cached is not None and cached[0] == (pos._version, crd._version, pos.data_ptr()):
+        return cached[1]
+    plan = AttnBandPlan(pos, crd)
+    crd._sb_attn_band_plan = ((pos._version, crd._version, pos.data_ptr()), plan)
+    return plan
+
+
+def attn_band_status() -> int:
+    """0 unless a tensor-core wait of the band kernel ran out since the library was loaded
+    (synchronises the device)."""
+    return int(_lib.lib().sb_attn_band_status())
+
+
+def attn_band_probe(Q: torch.Tensor, Kmat: torch.Tensor, V: Optional[torch.Tensor] = None, tile: int = 0):
+    """Self-test of the tcgen05 path on one tile, every window column counted as stored, scale 1.
+    Returns (raw, image): raw = the 128 x 384 products of rows [128 tile, +128) of Q with the rows
+    of Kmat in the tile's window (zeros outside the matrices); image = the tile's 128 x 512
+    tensor-memory cells at the end (hi parts of P, unnormalised P V, lo parts of P's last 64
+    columns)."""
+    Q, Kmat = _dev(Q, torch.float32, "Q").contiguous(), _dev(Kmat, torch.float32, "K").contiguous()
+    V = Kmat if V is None else _dev(V, torch.float32, "V").contiguous()
+    if Q.dim() != 2 or Kmat.dim() != 2 or Q.shape[1] != 64 or Kmat.shape[1] != 64 or V.shape != Kmat.shape:
+        raise ValueError("Q must be (rows, 64), K and V (cols, 64)")
+    raw = torch.zeros((AttnBandPlan.ROWS, AttnBandPlan.COLS), dtype=torch.float32, device=Q.device)
+    image = torch.zeros((AttnBandPlan.ROWS, 512), dtype=torch.float32, device=Q.device)
+    with torch.cuda.device(Q.device):
+        check(_lib.lib().sb_attn_band_probe(Q.shape[0], Kmat.shape[0], 64, int(tile), Q.data_ptr(), 64,
+                                            Kmat.data_ptr(), 64, V.data_ptr(), 64, raw.data_ptr(),
+                                            image.data_ptr(), _stream()))
+    return _wrote(raw), _wrote(image)
+
+
 FUSED_ATTENTION_D = (32, 64)
 
 
@@ -166,13 +239,15 @@ def _mask_is_all_ones(mask_val: torch.Tensor) -> bool:
 
 
 def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
-                         attn_plan: Optional[AttnPlan] = None,
+                         attn_plan: Optional[Union[AttnPlan, AttnBandPlan]] = None,
                          out: Optional[torch.Tensor] = None, stages: int = 3) -> torch.Tensor:
     """O = softmax_rows(scale * mask_val .* (Q Kmat^T) on the stored entries) V in one call, the
     scores never written out.  Q: (m, d) or (batch, m, d); Kmat, V: (n, d) or (batch, n, d); head
     dimension d in FUSED_ATTENTION_D.  Rows without stored entries give zero rows.
+    ``attn_plan``: an ``AttnPlan`` (16x16 blocks, mma.sync) or an ``AttnBandPlan`` (128-row tiles of
+    a band on tcgen05, d = 64); default: the block plan.
     ``stages``: 3 = the whole call; 1, 2 = its two kernels one by one (scattered entries, then
-    blocks; same arguments and ``out``), for callers that time them."""
+    blocks / tiles; same arguments and ``out``), for callers that time them."""
     pos = _dev(pos, torch.int32, "pos")
     crd = _dev(crd, torch.int32, "crd")
     m, nnz = pos.numel() - 1, crd.numel()
@@ -203,6 +278,16 @@ def sparse_attention_csr(pos, crd, mask_val, Q, Kmat, V, scale: float = 1.0,
     L = _lib.lib()
     sbytes = L.sb_sparse_attention_scratch_bytes(m, attn_plan.rem_nnz, batch)
     scratch = attn_plan.scratch(sbytes) if sbytes else None
+    if isinstance(attn_plan, AttnBandPlan):
+        if d != 64:
+            raise ValueError("the band path needs head dimension 64")
+        with torch.cuda.device(Q.device):
+            check(L.sb_sparse_attention_band_f32(m, n, d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val),
+                                                 Q.data_ptr(), d, Kmat.data_ptr(), d, V.data_ptr(), d,
+                                                 float(scale), out.data_ptr(), d, batch, m * d, n * d, n * d,
+                                                 m * d, attn_plan.buf.data_ptr(), attn_plan.rem_nnz,
+                                                 _ptr(scratch), sbytes, int(stages), _stream()))
+        return _wrote(out)
     with torch.cuda.device(Q.device):
         check(L.sb_sparse_attention_csr_f32(m, n, d, nnz, pos.data_ptr(), crd.data_ptr(), _ptr(mask_val),
                                             Q.data_ptr(), d, Kmat.data_ptr(), d, V.data_ptr(), d,

@@ -13,6 +13,7 @@ on the device end to end.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -27,11 +28,22 @@ def attention_block_plan(pos: torch.Tensor, crd: torch.Tensor) -> Optional[K.Blo
     return bp if bp.dense_fraction >= K.BLOCKED_MIN_DENSE_FRACTION else None
 
 
-def attention_plan(pos: torch.Tensor, crd: torch.Tensor, d: int, dv: int) -> Optional[K.AttnPlan]:
-    """The mask's attention plan if the one-call path applies: square mask, head dimension 32 / 64
-    for Q, K and V, and enough of the mask in well-filled 16x16 blocks; else None."""
+BAND_MIN_INSIDE_FRACTION = 0.5   # share of the mask inside the tiles' windows ...
+BAND_MIN_WINDOW_FILL = 0.25      # ... and share of the window cells that are stored, for the band path
+
+
+def attention_plan(pos: torch.Tensor, crd: torch.Tensor, d: int, dv: int):
+    """The mask's plan if the one-call path applies (square mask, head dimension 32 / 64 for Q, K
+    and V), else None: a ``kernels.AttnBandPlan`` (128-row tiles on tcgen05) for head dimension 64
+    when most of the mask lies in well-filled windows around the diagonal, else a
+    ``kernels.AttnPlan`` when enough of the mask sits in well-filled 16x16 blocks.
+    SCORCH_B200_NO_BAND=1 leaves the band path out."""
     if d != dv or d not in K.FUSED_ATTENTION_D:
         return None
+    if d == 64 and not os.environ.get("SCORCH_B200_NO_BAND"):
+        bp = K.attn_band_plan_for(pos, crd)
+        if bp.inside_fraction >= BAND_MIN_INSIDE_FRACTION and bp.window_fill >= BAND_MIN_WINDOW_FILL:
+            return bp
     ap = K.attn_plan_for(pos, crd)
     return ap if ap.block_fraction >= K.BLOCKED_MIN_DENSE_FRACTION else None
 
