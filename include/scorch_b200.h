@@ -308,7 +308,10 @@ SB_API int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t 
  *                          products Q K^T; `tmem_image` (may be null) the tile's 128 x 512
  *                          tensor-memory cells at the end: columns [0,384) the hi parts of
  *                          P = exp2(log2(e) S - row max), [384,448) the unnormalised O = P V,
- *                          [448,512) the lo parts of P's last 64 columns.  O is not written.
+ *                          [448,512) the lo parts of P's last 64 columns; `phase_clocks` (may be
+ *                          null, 36 values; the scores are then not copied out) the SM clock at the kernel's phase boundaries (scores
+ *                          staged and issued piece by piece, row maxima, the six rounds of
+ *                          O += P V, end).  O is not written.
  * -------------------------------------------------------------------------------------------- */
 #define SB_ATTN_BAND_ROWS 128
 #define SB_ATTN_BAND_COLS 384
@@ -327,7 +330,8 @@ SB_API int sb_sparse_attention_band_f32(int64_t m, int64_t n, int64_t d, int64_t
                                         void* stream);
 SB_API int sb_attn_band_probe(int64_t m, int64_t n, int64_t d, int64_t tile, const float* Q,
                               int64_t ldq, const float* K, int64_t ldk, const float* V, int64_t ldv,
-                              float* raw_scores, float* tmem_image, void* stream);
+                              float* raw_scores, float* tmem_image, long long* phase_clocks,
+                              void* stream);
 SB_API int sb_attn_band_status(void);
 
 /* --------------------------------------------------------------------------------------------

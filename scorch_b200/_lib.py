@@ -68,7 +68,8 @@ SIGNATURES = {
     "sb_sparse_attention_band_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                             _i64, _ptr, _i64, _f32, _ptr, _i64, _i64, _i64, _i64, _i64,
                                             _i64, _ptr, _i64, _ptr, _sz, _int, _ptr]),
-    "sb_attn_band_probe": (_int, [_i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr]),
+    "sb_attn_band_probe": (_int, [_i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _ptr, _i64, _ptr, _ptr, _ptr,
+                                  _ptr]),
     "sb_attn_band_status": (_int, []),
     "sb_csr_row_softmax_f32": (_int, [_i64, _i64, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr]),
     "sb_spgemm_workspace_bytes": (_sz, [_i64, _i64, _int]),

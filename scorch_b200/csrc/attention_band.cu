@@ -34,7 +34,8 @@ namespace sb {
 constexpr int kBandRows = SB_ATTN_BAND_ROWS;    // mask rows per tile
 constexpr int kBandCols = SB_ATTN_BAND_COLS;    // columns of a tile's window
 constexpr int kBandWords = kBandCols / 32;      // 32-bit words of a row's stored-column mask
-constexpr int kBandThreads = 256;
+constexpr int kBandWorkWarps = 8;              // warps that stage operands and do the softmax
+constexpr int kBandThreads = (kBandWorkWarps + 1) * 32;   // + one warp whose lane 0 issues the tensor-core work
 constexpr int kTmemCols = 512;
 constexpr int kTmemO = 384;                     // first TMEM column of the output accumulator
 constexpr int kTmemPlo = 448;                   // first TMEM column of the lo parts of P
@@ -235,6 +236,8 @@ struct BandArgs {
   float* raw_scores;   // probe only: the tile's 128 x 384 products Q K^T, unscaled and unmasked
   float* tmem_image;   // probe only: the tile's 128 x 512 tensor-memory cells after the last O += P V
   int probe_tile;
+  long long* clocks;   // probe only: clock64() of thread 0 at the kernel's phase boundaries
+  int last_entry;      // nnz - 1 (bound of the mask-value reads)
 };
 
 // Rows [row0, row0 + ROWS) of a row-major matrix (row pitch ld floats, rows outside [0, limit)
@@ -242,37 +245,45 @@ struct BandArgs {
 // group the 16-byte pieces (4 features) of the 8 rows are contiguous (128 bytes per core matrix),
 // the D / 4 cores of the group side by side.  Lanes: 8 rows x 4 neighbouring cores = 512
 // contiguous bytes of shared memory per warp store, 64 contiguous bytes of each row per load.
+// Two halves, so that a piece can be loaded into registers while the buffer it goes to is still
+// being read by the tensor cores.
 template <int D, int ROWS>
-__device__ __forceinline__ void band_stage(float* __restrict__ hi, float* __restrict__ lo,
-                                           const float* __restrict__ src, unsigned ld, int row0, int limit) {
-  constexpr int QG = D / 16;                       // groups of 4 cores per row group
-  constexpr int TASKS = (ROWS / 8) * QG;           // (row group, core group) pairs, one per warp pass
-  constexpr int PASSES = TASKS / (kBandThreads / 32);
-  static_assert(TASKS % (kBandThreads / 32) == 0, "staging tasks must divide over the warps");
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r8 = lane & 7, q4 = lane >> 3;
+struct BandPiece {
+  static constexpr int QG = D / 16;                       // groups of 4 cores per row group
+  static constexpr int TASKS = (ROWS / 8) * QG;           // (row group, core group) pairs, one per warp pass
+  static constexpr int PASSES = TASKS / kBandWorkWarps;
+  static_assert(TASKS % kBandWorkWarps == 0, "staging tasks must divide over the warps");
   float4 v[PASSES];
+
+  __device__ __forceinline__ void load(const float* __restrict__ src, unsigned ld, int row0, int limit) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r8 = lane & 7, q4 = lane >> 3;
 #pragma unroll
-  for (int i = 0; i < PASSES; i++) {
-    const int task = i * (kBandThreads / 32) + warp;
-    const int rg = task / QG, core = (task % QG) * 4 + q4;
-    const int row = row0 + rg * 8 + r8;
-    v[i] = (row >= 0 && row < limit)
-               ? __ldg(reinterpret_cast<const float4*>(src + (size_t)((unsigned long long)(unsigned)row * ld) + core * 4))
-               : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < PASSES; i++) {
+      const int task = i * kBandWorkWarps + warp;
+      const int rg = task / QG, core = (task % QG) * 4 + q4;
+      const int row = row0 + rg * 8 + r8;
+      v[i] = (row >= 0 && row < limit)
+                 ? __ldg(reinterpret_cast<const float4*>(src + (size_t)((unsigned long long)(unsigned)row * ld) + core * 4))
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
+  __device__ __forceinline__ void store(float* __restrict__ hi, float* __restrict__ lo) const {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r8 = lane & 7, q4 = lane >> 3;
 #pragma unroll
-  for (int i = 0; i < PASSES; i++) {
-    const int task = i * (kBandThreads / 32) + warp;
-    const int rg = task / QG, core = (task % QG) * 4 + q4;
-    const int off = rg * 8 * D + core * 32 + r8 * 4;
-    uint4 h, l;
-    attn_split(v[i].x, h.x, l.x); attn_split(v[i].y, h.y, l.y);
-    attn_split(v[i].z, h.z, l.z); attn_split(v[i].w, h.w, l.w);
-    *reinterpret_cast<uint4*>(hi + off) = h;
-    *reinterpret_cast<uint4*>(lo + off) = l;
+    for (int i = 0; i < PASSES; i++) {
+      const int task = i * kBandWorkWarps + warp;
+      const int rg = task / QG, core = (task % QG) * 4 + q4;
+      const int off = rg * 8 * D + core * 32 + r8 * 4;
+      uint4 h, l;
+      attn_split(v[i].x, h.x, l.x); attn_split(v[i].y, h.y, l.y);
+      attn_split(v[i].z, h.z, l.z); attn_split(v[i].w, h.w, l.w);
+      *reinterpret_cast<uint4*>(hi + off) = h;
+      *reinterpret_cast<uint4*>(lo + off) = l;
+    }
   }
-}
+};
 
 // 64 rows [row0, row0 + 64) of V (row pitch ld floats, rows outside [0, limit) read as zeros) ->
 // hi / lo parts of their transpose in the same canonical layout: "rows" are now the D features,
@@ -283,48 +294,59 @@ __device__ __forceinline__ void band_stage(float* __restrict__ hi, float* __rest
 // per load) and stores them as one 16-byte piece; the 8 lanes of a feature group fill one core
 // matrix, so the stores are free of bank conflicts.
 template <int D>
-__device__ __forceinline__ void band_stage_transposed(float* __restrict__ hi, float* __restrict__ lo,
-                                                      const float* __restrict__ src, unsigned ld, int row0,
-                                                      int limit) {
-  constexpr int ITEMS = (D / 32) * 2;   // (32-feature half, 4-column block) pairs per thread: 16 blocks over 8 warps
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+struct BandPieceT {
+  static constexpr int HALVES = D / 32;
+  static constexpr int ITEMS = HALVES * 2;   // (32-feature half, 4-column block) pairs per thread: 16 blocks over 8 warps
   float v[ITEMS][4];
+
+  __device__ __forceinline__ void load(const float* __restrict__ src, unsigned ld, int row0, int limit) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int it = 0; it < ITEMS; it++) {
-    const int f = (it % (D / 32)) * 32 + lane, jb = warp * 2 + it / (D / 32);
+    for (int it = 0; it < ITEMS; it++) {
+      const int f = (it % HALVES) * 32 + lane, jb = warp * 2 + it / HALVES;
 #pragma unroll
-    for (int jj = 0; jj < 4; jj++) {
-      const int row = row0 + jb * 4 + jj;
-      v[it][jj] = (row >= 0 && row < limit) ? __ldg(src + (size_t)((unsigned long long)(unsigned)row * ld) + f) : 0.f;
+      for (int jj = 0; jj < 4; jj++) {
+        const int row = row0 + jb * 4 + jj;
+        v[it][jj] = (row >= 0 && row < limit) ? __ldg(src + (size_t)((unsigned long long)(unsigned)row * ld) + f) : 0.f;
+      }
     }
   }
+  __device__ __forceinline__ void store(float* __restrict__ hi, float* __restrict__ lo) const {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int it = 0; it < ITEMS; it++) {
-    const int f = (it % (D / 32)) * 32 + lane, jb = warp * 2 + it / (D / 32);
-    const int off = (f >> 3) * (16 * 32) + jb * 32 + (f & 7) * 4;   // floats
-    uint4 h, l;
-    attn_split(v[it][0], h.x, l.x); attn_split(v[it][1], h.y, l.y);
-    attn_split(v[it][2], h.z, l.z); attn_split(v[it][3], h.w, l.w);
-    *reinterpret_cast<uint4*>(hi + off) = h;
-    *reinterpret_cast<uint4*>(lo + off) = l;
+    for (int it = 0; it < ITEMS; it++) {
+      const int f = (it % HALVES) * 32 + lane, jb = warp * 2 + it / HALVES;
+      const int off = (f >> 3) * (16 * 32) + jb * 32 + (f & 7) * 4;   // floats
+      uint4 h, l;
+      attn_split(v[it][0], h.x, l.x); attn_split(v[it][1], h.y, l.y);
+      attn_split(v[it][2], h.z, l.z); attn_split(v[it][3], h.w, l.w);
+      *reinterpret_cast<uint4*>(hi + off) = h;
+      *reinterpret_cast<uint4*>(lo + off) = l;
+    }
   }
-}
+};
 
 template <int D>
 __global__ void __launch_bounds__(kBandThreads, 1)
 attn_band_kernel(AttnArgs a, BandArgs b) {
   extern __shared__ __align__(128) unsigned char band_smem[];
-  constexpr int TILE_FLOATS = kBandRows * D;           // one 128 x D operand part
+  constexpr int TILE_FLOATS = kBandRows * D;           // one 128 x D operand part (hi or lo)
+  constexpr int VT_FLOATS = 64 * D;                    // one part of a transposed 64-row piece of V
   constexpr uint32_t GROUP_BYTES = 8 * D * 4;          // an 8-row group: stride between row groups
+  constexpr uint32_t VT_GROUP_BYTES = (64 / 4) * 128;  // 8 features x 64 window columns of V^T
   constexpr uint32_t CORE_BYTES = 128;                 // a core matrix: stride between neighbouring cores
   constexpr int KSTEPS = D / 8;                        // tcgen05.mma steps over the head dimension
+  constexpr int ROUNDS = kBandCols / 64;               // O += P V, 64 window columns per round
   float* q_hi = reinterpret_cast<float*>(band_smem);
   float* q_lo = q_hi + TILE_FLOATS;
-  float* x_hi = q_lo + TILE_FLOATS;
-  float* x_lo = x_hi + TILE_FLOATS;
-  float* s_red = x_lo + TILE_FLOATS;                   // [2][128] row maxima, then row sums
-  unsigned long long* bar = reinterpret_cast<unsigned long long*>(s_red + 2 * kBandRows);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  float* kbuf = q_lo + TILE_FLOATS;                    // two K pieces (hi, lo each) = four V^T pieces
+  float* s_red = kbuf + 4 * TILE_FLOATS;               // [2][128] row maxima, then row sums
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(s_red + 2 * kBandRows);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  auto k_hi = [&](int i) { return kbuf + i * 2 * TILE_FLOATS; };
+  auto k_lo = [&](int i) { return kbuf + i * 2 * TILE_FLOATS + TILE_FLOATS; };
+  auto v_hi = [&](int i) { return kbuf + i * 2 * VT_FLOATS; };
+  auto v_lo = [&](int i) { return kbuf + i * 2 * VT_FLOATS + VT_FLOATS; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = b.raw_scores ? b.probe_tile : (int)blockIdx.x;
@@ -335,10 +357,13 @@ attn_band_kernel(AttnArgs a, BandArgs b) {
   const float* K = a.K + bz * a.stride_k;
   const float* V = a.V + bz * a.stride_v;
   float* O = a.O + bz * a.stride_o;
-  const uint32_t bar_addr = smem_u32(bar);
+  // mbarriers: [0], [1] = the tensor cores are done with K piece buffer 0 / 1; [2] = with a round of O += P V
+  const uint32_t bar_k0 = smem_u32(bars), bar_k1 = smem_u32(bars + 1), bar_pv = smem_u32(bars + 2);
 
   if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_k0) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_k1) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_pv) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -350,144 +375,246 @@ attn_band_kernel(AttnArgs a, BandArgs b) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  uint32_t phase = 0;
-  bool failed = false;
+  int mark_i = 0;
+  auto mark = [&]() {
+    if (b.clocks && threadIdx.x == 0) b.clocks[mark_i] = clock64();
+    mark_i++;
+  };
+  mark();   // 0
 
   constexpr uint32_t IDESC_S = umma_idesc_tf32(kBandRows, 128, 0);
   constexpr uint32_t IDESC_O = umma_idesc_tf32(kBandRows, D, 0);
-  constexpr uint32_t VT_GROUP_BYTES = (64 / 4) * 128;   // 8 features x 64 window columns of V^T
 
-  // ---- S = Q K^T, 128 window columns at a time ---------------------------------------------------------
-  band_stage<D, kBandRows>(q_hi, q_lo, Q, a.ldq, i0, a.m);
-#pragma unroll 1
-  for (int c = 0; c < kBandCols / 128 && !failed; c++) {
-    band_stage<D, 128>(x_hi, x_lo, K, a.ldk, c0 + c * 128, b.n);
-    async_proxy_fence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      tc_fence_after();
-      const uint32_t qh = smem_u32(q_hi), ql = smem_u32(q_lo), kh = smem_u32(x_hi), kl = smem_u32(x_lo);
-      const uint32_t d_tmem = tmem + (uint32_t)(c * 128);
-#pragma unroll
-      for (int pass = 0; pass < 3; pass++) {
-        const uint32_t aa = pass == 0 ? ql : qh, bb = pass == 1 ? kl : kh;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++)
-          umma_ss(d_tmem, umma_desc(aa + ks * 2 * CORE_BYTES, CORE_BYTES, GROUP_BYTES),
-                  umma_desc(bb + ks * 2 * CORE_BYTES, CORE_BYTES, GROUP_BYTES), IDESC_S,
-                  (pass | ks) != 0 ? 1u : 0u);
-      }
-      umma_commit(bar_addr);
-    }
-    failed = !mbar_wait(bar_addr, phase);
-    phase ^= 1u;
-    failed = __syncthreads_or(failed) != 0;
+  // Descriptors of the operand parts, built once; a k-step moves the start address by two cores
+  // (2 * 128 bytes = 16 units of 16 bytes), which is a plain addition on the descriptor.
+  const uint64_t dq_hi = umma_desc(smem_u32(q_hi), CORE_BYTES, GROUP_BYTES);
+  const uint64_t dq_lo = umma_desc(smem_u32(q_lo), CORE_BYTES, GROUP_BYTES);
+  constexpr uint64_t KSTEP = (2 * CORE_BYTES) >> 4;
+  // S[:, 128 c .. 128 c + 127] = Q K_c^T from K piece buffer `buf` (one thread; three passes of the split)
+  auto issue_scores = [&](int c, int buf, uint32_t bar) {
     tc_fence_after();
-  }
+    const uint64_t dk_hi = umma_desc(smem_u32(k_hi(buf)), CORE_BYTES, GROUP_BYTES);
+    const uint64_t dk_lo = umma_desc(smem_u32(k_lo(buf)), CORE_BYTES, GROUP_BYTES);
+    const uint32_t d_tmem = tmem + (uint32_t)(c * 128);
+#pragma unroll
+    for (int pass = 0; pass < 3; pass++) {
+      const uint64_t aa = pass == 0 ? dq_lo : dq_hi, bb = pass == 1 ? dk_lo : dk_hi;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ks++)
+        umma_ss(d_tmem, aa + ks * KSTEP, bb + ks * KSTEP, IDESC_S, (pass | ks) != 0 ? 1u : 0u);
+    }
+    umma_commit(bar);
+  };
+  // every thread waits; the outcome is made uniform over the CTA
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    const bool ok = mbar_wait(bar, parity);
+    const bool bad = __syncthreads_or(!ok) != 0;
+    tc_fence_after();
+    return bad;
+  };
 
-  // this thread's row and columns: row = TMEM lane; columns 64 g + 32 h + [0, 32) for g = 0..5
+  // roles: warps 0..7 stage operands and own the rows (row = TMEM lane; columns 64 g + 32 h + [0, 32)
+  // for g = 0..5); lane 0 of warp 8 issues the tensor-core work, so that issuing overlaps the others' work
+  const bool worker = warp < kBandWorkWarps;
+  const bool issuer = threadIdx.x == kBandWorkWarps * 32;
   const int lane_base = 32 * (warp & 3);
-  const int r = lane_base + lane, h = warp >> 2;
+  const int r = lane_base + lane, h = (warp >> 2) & 1;
   const int row = i0 + r;
-  const bool live = row < a.m;
+  const bool live = worker && row < a.m;
   const uint32_t t_row = tmem + ((uint32_t)lane_base << 16);
   const float scale = a.scale * 1.4426950408889634f;   // scores in log2 units
-  float mx = -INFINITY;
+  float M_s = -INFINITY, L_s = 0.f, ms = 0.f, sum = 0.f;
+  bool failed = false;
 
-  if (!failed) {
+  do {
+    // ---- S = Q K^T: K pieces of 128 window columns through two buffers; pieces are loaded into
+    // registers ahead of the point where their buffer is free ------------------------------------------------
+    BandPiece<D, kBandRows> pq;
+    BandPiece<D, 128> pk0, pk1;
+    if (worker) {
+      pq.load(Q, a.ldq, i0, a.m);
+      pk0.load(K, a.ldk, c0, b.n);
+      pk1.load(K, a.ldk, c0 + 128, b.n);
+      pq.store(q_hi, q_lo);
+      pk0.store(k_hi(0), k_lo(0));
+    }
+    async_proxy_fence();
+    __syncthreads();
+    mark();   // 1: Q and K piece 0 staged
+    if (issuer) issue_scores(0, 0, bar_k0);
+    if (worker) {
+      pk0.load(K, a.ldk, c0 + 256, b.n);                // piece 2, for buffer 0 once piece 0 is consumed
+      pk1.store(k_hi(1), k_lo(1));
+    }
+    async_proxy_fence();
+    __syncthreads();
+    mark();   // 2: K piece 1 staged
+    if (issuer) issue_scores(1, 1, bar_k1);
+    // ---- what the row maxima and the probabilities need: stored-column bits, mask values ---------------------
     unsigned words[kBandWords];
 #pragma unroll
     for (int w = 0; w < kBandWords; w++)
       words[w] = !live ? 0u : b.bits ? __ldg(b.bits + (size_t)row * kBandWords + w) : 0xffffffffu;  // (probe: all stored)
     const float* mask_val = (a.mask_val && !__ldg(a.mask_is_ones)) ? a.mask_val : nullptr;
-    int ep = (live && b.ent0) ? __ldg(b.ent0 + row) : 0;
-    // ---- scores: scale, mask values, -inf where nothing is stored; row maximum -------------------------
+    const int ent0 = (live && b.ent0) ? __ldg(b.ent0 + row) : 0;
+    // scores of a 32-column chunk: scaled, times the mask value, -inf where nothing is stored.
+    // Without branches: lanes differ in which columns are stored.  `ep` walks the row's entries
+    // (their mask values); it is only dereferenced for stored columns' positions, clamped to `last`.
+    const int last = b.last_entry;
+    auto masked = [&](const float (&v)[32], unsigned word, int& ep, float (&sc)[32]) {
+      if (mask_val) {
 #pragma unroll
-    for (int g = 0; g < kBandCols / 64; g++) {
-      if (h == 1) ep += __popc(words[2 * g]);
-      const unsigned word = h ? words[2 * g + 1] : words[2 * g];
-      const int cb = g * 64 + h * 32;
-      float v[32];
-      tmem_ld32(t_row + (uint32_t)cb, v);
-      if (b.raw_scores) {
-#pragma unroll
-        for (int j = 0; j < 32; j++) b.raw_scores[(size_t)r * kBandCols + cb + j] = v[j];
-      }
-      uint32_t out[32];
-#pragma unroll
-      for (int j = 0; j < 32; j++) {
-        float s = -INFINITY;
-        if ((word >> j) & 1u) {
-          s = v[j] * scale;
-          if (mask_val) s *= __ldg(mask_val + ep);
-          ep++;
+        for (int j = 0; j < 32; j++) {
+          const bool on = (word >> j) & 1u;
+          const float w = __ldg(mask_val + min(ep, last));
+          sc[j] = on ? v[j] * scale * w : -INFINITY;
+          ep += on;
         }
-        mx = fmaxf(mx, s);
-        out[j] = __float_as_uint(s);
-      }
-      tmem_st32(t_row + (uint32_t)cb, out);
-      if (h == 0) ep += __popc(words[2 * g + 1]);
-    }
-    tmem_st_wait();
-  }
-  s_red[h * kBandRows + r] = mx;
-  __syncthreads();
-  float M_s = -INFINITY, L_s = 0.f;
-  if (a.has_rem && live) {
-    const float2 st = __ldg(a.stats + bz * a.m + row);
-    M_s = st.x;
-    L_s = st.y;
-  }
-  const float mt = fmaxf(fmaxf(s_red[r], s_red[kBandRows + r]), M_s);
-  const float ms = (mt == -INFINITY) ? 0.f : mt;
-  __syncthreads();   // (s_red is reused for the sums)
-
-  // ---- O += P V, 64 window columns at a time -----------------------------------------------------------
-  float sum = 0.f;
-#pragma unroll 1
-  for (int g = 0; g < kBandCols / 64 && !failed; g++) {
-    band_stage_transposed<D>(x_hi, x_lo, V, a.ldv, c0 + g * 64, b.n);
-    const int cb = g * 64 + h * 32;
-    float v[32];
-    tmem_ld32(t_row + (uint32_t)cb, v);
-    uint32_t ph[32], pl[32];
+      } else {
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      const float p = attn_exp2(v[j] - ms);
-      sum += p;
-      attn_split(p, ph[j], pl[j]);
+        for (int j = 0; j < 32; j++) sc[j] = ((word >> j) & 1u) ? v[j] * scale : -INFINITY;
+      }
+    };
+    float mx = -INFINITY;
+    int ep_max = ent0;
+    // maxima of the scores of K piece c (rounds 2 c and 2 c + 1), once that piece's products are done
+    auto row_max_piece = [&](int c) {
+      if (!worker) return;
+#pragma unroll
+      for (int gg = 0; gg < 2; gg++) {
+        const int g = 2 * c + gg;
+        const unsigned w0 = g == 0 ? words[0] : g == 1 ? words[2] : g == 2 ? words[4] : g == 3 ? words[6]
+                                              : g == 4 ? words[8] : words[10];
+        const unsigned w1 = g == 0 ? words[1] : g == 1 ? words[3] : g == 2 ? words[5] : g == 3 ? words[7]
+                                              : g == 4 ? words[9] : words[11];
+        if (h == 1) ep_max += __popc(w0);
+        const int cb = g * 64 + h * 32;
+        float v[32], sc[32];
+        tmem_ld32(t_row + (uint32_t)cb, v);
+        if (b.raw_scores && !b.clocks) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) b.raw_scores[(size_t)r * kBandCols + cb + j] = v[j];
+        }
+        masked(v, h ? w1 : w0, ep_max, sc);
+#pragma unroll
+        for (int j = 0; j < 32; j++) mx = fmaxf(mx, sc[j]);
+        if (h == 0) ep_max += __popc(w1);
+      }
+    };
+    BandPieceT<D> pv0, pv1;
+    if (worker) {
+      pv0.load(V, a.ldv, c0, b.n);
+      pv1.load(V, a.ldv, c0 + 64, b.n);
     }
-    tmem_st32(t_row + (uint32_t)cb, ph);
-    tmem_st32(t_row + (uint32_t)(kTmemPlo + h * 32), pl);
-    tmem_st_wait();
+    if ((failed = wait_all(bar_k0, 0u))) break;          // piece 0 consumed
+    mark();   // 3
+    if (worker) pk0.store(k_hi(0), k_lo(0));
     async_proxy_fence();
-    tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) {
-      tc_fence_after();
-      const uint32_t vh = smem_u32(x_hi), vl = smem_u32(x_lo);
-      const uint32_t d_tmem = tmem + (uint32_t)kTmemO;
-#pragma unroll
-      for (int pass = 0; pass < 3; pass++) {
-        const uint32_t a_tmem = tmem + (uint32_t)(pass == 0 ? kTmemPlo : g * 64);
-        const uint32_t bb = pass == 1 ? vl : vh;
-#pragma unroll
-        for (int ks = 0; ks < 8; ks++)
-          umma_ts(d_tmem, a_tmem + (uint32_t)(ks * 8), umma_desc(bb + ks * 2 * CORE_BYTES, CORE_BYTES, VT_GROUP_BYTES),
-                  IDESC_O, (g | pass | ks) != 0 ? 1u : 0u);
-      }
-      umma_commit(bar_addr);
+    mark();   // 4: K piece 2 staged
+    if (issuer) issue_scores(2, 0, bar_k0);
+    row_max_piece(0);
+    if ((failed = wait_all(bar_k1, 0u))) break;          // piece 1 consumed: V^T buffers 2 and 3 are free
+    mark();   // 5
+    if (worker) {
+      pv0.store(v_hi(2), v_lo(2));
+      pv1.store(v_hi(3), v_lo(3));
+      pv0.load(V, a.ldv, c0 + 128, b.n);
+      pv1.load(V, a.ldv, c0 + 192, b.n);
     }
-    failed = !mbar_wait(bar_addr, phase);
-    phase ^= 1u;
-    failed = __syncthreads_or(failed) != 0;
-    tc_fence_after();
-  }
+    row_max_piece(1);
+    mark();   // 6: V^T pieces 0, 1 staged, maxima of pieces 0 and 1
+    if ((failed = wait_all(bar_k0, 1u))) break;          // all scores are in tensor memory; buffers 0 and 1 free
+    mark();   // 7
+    if (worker) {
+      pv0.store(v_hi(0), v_lo(0));
+      pv1.store(v_hi(1), v_lo(1));
+    }
+    row_max_piece(2);
+    mark();   // 8: V^T pieces 2, 3 staged, all maxima
+
+    if (worker) s_red[h * kBandRows + r] = mx;
+    __syncthreads();
+    if (a.has_rem && live) {
+      const float2 st = __ldg(a.stats + bz * a.m + row);
+      M_s = st.x;
+      L_s = st.y;
+    }
+    if (worker) {
+      const float mt = fmaxf(fmaxf(s_red[r], s_red[kBandRows + r]), M_s);
+      ms = (mt == -INFINITY) ? 0.f : mt;
+    }
+    mark();   // 9: row maxima
+
+    // ---- O += P V, 64 window columns per round; V^T piece g sits in buffer (g + 2) % 4 -------------------
+    int ep = ent0;
+#pragma unroll 1
+    for (int g = 0; g < ROUNDS; g++) {
+      const int cb = g * 64 + h * 32;
+      uint32_t ph[32], pl[32];
+      if (worker) {
+        const unsigned w0 = g == 0 ? words[0] : g == 1 ? words[2] : g == 2 ? words[4] : g == 3 ? words[6]
+                                              : g == 4 ? words[8] : words[10];
+        const unsigned w1 = g == 0 ? words[1] : g == 1 ? words[3] : g == 2 ? words[5] : g == 3 ? words[7]
+                                              : g == 4 ? words[9] : words[11];
+        if (h == 1) ep += __popc(w0);
+        float v[32], sc[32];
+        tmem_ld32(t_row + (uint32_t)cb, v);
+        masked(v, h ? w1 : w0, ep, sc);
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const float p = attn_exp2(sc[j] - ms);
+          sum += p;
+          attn_split(p, ph[j], pl[j]);
+        }
+        if (h == 0) ep += __popc(w1);
+        // piece g + 3 goes to the buffer that round g - 1 releases below
+        if (g >= 1 && g + 3 < ROUNDS) pv0.load(V, a.ldv, c0 + (g + 3) * 64, b.n);
+      }
+      mark();   // 10 + 4 g: probabilities of the round in registers
+      // the round before must be done with the lo columns and with the V^T buffer that is refilled
+      if (g > 0 && (failed = wait_all(bar_pv, (uint32_t)((g - 1) & 1)))) break;
+      mark();   // 11 + 4 g: the round before is done
+      if (worker) {
+        tmem_st32(t_row + (uint32_t)cb, ph);
+        tmem_st32(t_row + (uint32_t)(kTmemPlo + h * 32), pl);
+        if (g >= 1 && g + 3 < ROUNDS) pv0.store(v_hi((g + 1) & 3), v_lo((g + 1) & 3));
+        tmem_st_wait();
+      }
+      async_proxy_fence();
+      tc_fence_before();
+      __syncthreads();
+      mark();   // 12 + 4 g: probabilities in tensor memory
+      if (issuer) {
+        tc_fence_after();
+        const int vb = (g + 2) & 3;
+        const uint64_t dv_hi = umma_desc(smem_u32(v_hi(vb)), CORE_BYTES, VT_GROUP_BYTES);
+        const uint64_t dv_lo = umma_desc(smem_u32(v_lo(vb)), CORE_BYTES, VT_GROUP_BYTES);
+        const uint32_t d_tmem = tmem + (uint32_t)kTmemO;
+        const uint32_t p_hi = tmem + (uint32_t)(g * 64), p_lo = tmem + (uint32_t)kTmemPlo;
+        const uint32_t later = g != 0 ? 1u : 0u;
+#pragma unroll
+        for (int pass = 0; pass < 3; pass++) {
+          const uint32_t a_tmem = pass == 0 ? p_lo : p_hi;
+          const uint64_t bb = pass == 1 ? dv_lo : dv_hi;
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++)
+            umma_ts(d_tmem, a_tmem + (uint32_t)(ks * 8), bb + ks * KSTEP, IDESC_O, (pass | ks) != 0 ? 1u : later);
+        }
+        umma_commit(bar_pv);
+      }
+      mark();   // 13 + 4 g
+    }
+    if (failed) break;
+    if ((failed = wait_all(bar_pv, (uint32_t)((ROUNDS - 1) & 1)))) break;
+    mark();   // 34
+  } while (false);
 
   // ---- epilogue: merge the scattered entries' (max, sum, O), normalise, write --------------------------
-  s_red[h * kBandRows + r] = sum;
   __syncthreads();
-  if (!failed && !b.raw_scores) {
+  if (worker) s_red[h * kBandRows + r] = sum;
+  __syncthreads();
+  if (!failed && !b.raw_scores && worker) {
     constexpr int HALF = D / 2;
     const float alpha = attn_exp2(M_s - ms);             // 0 for a row without scattered entries
     const float den = s_red[r] + s_red[kBandRows + r] + alpha * L_s;
@@ -509,7 +636,9 @@ attn_band_kernel(AttnArgs a, BandArgs b) {
       }
     }
   }
-  if (!failed && b.tmem_image) {
+  mark_i = 35;
+  mark();     // 35: output written
+  if (!failed && b.tmem_image && worker) {
 #pragma unroll 1
     for (int c = 0; c < kTmemCols / 64; c++) {
       float v[32];
@@ -527,7 +656,7 @@ attn_band_kernel(AttnArgs a, BandArgs b) {
 
 template <int D>
 static size_t band_smem_bytes() {
-  return (size_t)4 * kBandRows * D * 4 + 2 * kBandRows * 4 + 64;
+  return (size_t)6 * kBandRows * D * 4 + 2 * kBandRows * 4 + 64;
 }
 
 template <int D>
@@ -651,7 +780,7 @@ int sb_sparse_attention_band_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, c
     if (rc != SB_OK) return rc;
   }
   if (stages & SB_ATTN_STAGE_BLOCKS) {
-    BandArgs b = {(int)n, p.ent0, p.bits, nullptr, nullptr, 0};
+    BandArgs b = {(int)n, p.ent0, p.bits, nullptr, nullptr, 0, nullptr, (int)std::max<int64_t>(nnz - 1, 0)};
     rc = band_launch<64>(a, b, (unsigned)ceil_div(m, kBandRows), (unsigned)batch, st);
     if (rc != SB_OK) return rc;
   }
@@ -660,7 +789,7 @@ int sb_sparse_attention_band_f32(int64_t m, int64_t n, int64_t d, int64_t nnz, c
 
 int sb_attn_band_probe(int64_t m, int64_t n, int64_t d, int64_t tile, const float* Q, int64_t ldq,
                        const float* K, int64_t ldk, const float* V, int64_t ldv, float* raw_scores,
-                       float* tmem_image, void* stream) {
+                       float* tmem_image, long long* phase_clocks, void* stream) {
   int rc = band_check(m, n, d, 0, Q, ldq, K, ldk, V, ldv, raw_scores, d, 1, 0, 0, 0, 0);
   if (rc != SB_OK) return rc;
   SB_CHECK_ARG(tile >= 0 && tile < ceil_div(m, kBandRows), "attn_band_probe: tile out of range");
@@ -670,7 +799,7 @@ int sb_attn_band_probe(int64_t m, int64_t n, int64_t d, int64_t tile, const floa
   a.ldq = (unsigned)ldq; a.ldk = (unsigned)ldk; a.ldv = (unsigned)ldv; a.ldo = d;
   a.scale = 1.f;
   // (no plan: every window column counts as stored; O is not written)
-  BandArgs b = {(int)n, nullptr, nullptr, raw_scores, tmem_image, (int)tile};
+  BandArgs b = {(int)n, nullptr, nullptr, raw_scores, tmem_image, (int)tile, phase_clocks, 0};
   return band_launch<64>(a, b, 1u, 1u, (cudaStream_t)stream);
 }
 

@@ -204,23 +204,26 @@ def attn_band_status() -> int:
     return int(_lib.lib().sb_attn_band_status())
 
 
-def attn_band_probe(Q: torch.Tensor, Kmat: torch.Tensor, V: Optional[torch.Tensor] = None, tile: int = 0):
+def attn_band_probe(Q: torch.Tensor, Kmat: torch.Tensor, V: Optional[torch.Tensor] = None, tile: int = 0,
+                    with_clocks: bool = False):
     """Self-test of the tcgen05 path on one tile, every window column counted as stored, scale 1.
-    Returns (raw, image): raw = the 128 x 384 products of rows [128 tile, +128) of Q with the rows
+    Returns (raw, image, clocks): raw = the 128 x 384 products of rows [128 tile, +128) of Q with the rows
     of Kmat in the tile's window (zeros outside the matrices); image = the tile's 128 x 512
     tensor-memory cells at the end (hi parts of P, unnormalised P V, lo parts of P's last 64
-    columns)."""
+    columns); clocks (``with_clocks``; raw is then left zero) = 36 SM clock values at the kernel's phase
+    boundaries."""
     Q, Kmat = _dev(Q, torch.float32, "Q").contiguous(), _dev(Kmat, torch.float32, "K").contiguous()
     V = Kmat if V is None else _dev(V, torch.float32, "V").contiguous()
     if Q.dim() != 2 or Kmat.dim() != 2 or Q.shape[1] != 64 or Kmat.shape[1] != 64 or V.shape != Kmat.shape:
         raise ValueError("Q must be (rows, 64), K and V (cols, 64)")
     raw = torch.zeros((AttnBandPlan.ROWS, AttnBandPlan.COLS), dtype=torch.float32, device=Q.device)
     image = torch.zeros((AttnBandPlan.ROWS, 512), dtype=torch.float32, device=Q.device)
+    clocks = torch.zeros(36, dtype=torch.int64, device=Q.device) if with_clocks else None
     with torch.cuda.device(Q.device):
         check(_lib.lib().sb_attn_band_probe(Q.shape[0], Kmat.shape[0], 64, int(tile), Q.data_ptr(), 64,
                                             Kmat.data_ptr(), 64, V.data_ptr(), 64, raw.data_ptr(),
-                                            image.data_ptr(), _stream()))
-    return _wrote(raw), _wrote(image)
+                                            image.data_ptr(), _ptr(clocks), _stream()))
+    return _wrote(raw), _wrote(image), clocks
 
 
 FUSED_ATTENTION_D = (32, 64)

@@ -29,7 +29,7 @@ def attention_block_plan(pos: torch.Tensor, crd: torch.Tensor) -> Optional[K.Blo
 
 
 BAND_MIN_INSIDE_FRACTION = 0.5   # share of the mask inside the tiles' windows ...
-BAND_MIN_WINDOW_FILL = 0.25      # ... and share of the window cells that are stored, for the band path
+BAND_MIN_WINDOW_FILL = 0.5       # ... and share of the window cells that are stored, for the band path
 
 
 def attention_plan(pos: torch.Tensor, crd: torch.Tensor, d: int, dv: int):

@@ -153,8 +153,13 @@ def test_pipeline_picks_the_attention_call_and_matches_three_operators(oracle):
     mask = W.attention_mask(1024, window=64, density=0.01, seed=0)
     Q, Km, V = W.attention_qkv(1, 3, 1024, 64, seed=1)
     pos, crd, mv = dev(mask.pos), dev(mask.crd), dev(mask.val)
+    from scorch_b200 import kernels as K
     ap = P.attention_plan(pos, crd, 64, 64)
-    assert ap is not None and ap.block_fraction > 0.8
+    assert isinstance(ap, K.AttnPlan) and ap.block_fraction > 0.8     # +-64 fills a third of a 384-column window
+    wide = W.attention_mask(1024, window=128, density=0.01, seed=0)
+    bp = P.attention_plan(dev(wide.pos), dev(wide.crd), 64, 64)        # +-128 fills two thirds: the tcgen05 path
+    assert isinstance(bp, K.AttnBandPlan) and bp.inside_fraction > 0.9 and bp.window_fill > 0.5
+    assert isinstance(P.attention_plan(dev(wide.pos), dev(wide.crd), 32, 32), K.AttnPlan)
     assert P.attention_plan(pos, crd, 128, 128) is None and P.attention_plan(pos, crd, 64, 32) is None
     O = P.sparse_attention(pos, crd, mv, dev(Q), dev(Km), dev(V), scale=0.125)
     O3 = P.sparse_attention(pos, crd, mv, dev(Q), dev(Km), dev(V), scale=0.125, fused=False)

@@ -44,7 +44,7 @@ def test_probe_tensor_memory_image():
     Q = torch.randn((128, 64), generator=gen, device="cuda") * 0.5
     Km = torch.randn((384, 64), generator=gen, device="cuda") * 0.5
     V = torch.randn((384, 64), generator=gen, device="cuda")
-    raw, image = K.attn_band_probe(Q, Km, V, tile=0)
+    raw, image, _ = K.attn_band_probe(Q, Km, V, tile=0)
     assert K.attn_band_status() == 0
     S = (Q.double() @ Km.double().T) * 1.4426950408889634
     P = torch.exp2(S - S.max(1, keepdim=True).values)

@@ -59,6 +59,31 @@ def test_c2_full_sparse_attention(oracle):
               f"attention output head {u}")
 
 
+def test_c2_full_one_call_attention_both_tensor_core_paths(oracle):
+    """Configuration 2 at full size through the single attention call: the plan the pipeline picks
+    (128-row tiles on tcgen05) and the 16x16-block plan agree with each other, rows of the output
+    are convex combinations of V rows (linearity in V), and three heads match the oracle."""
+    from scorch_b200 import kernels as K, pipelines as P, workloads as W
+    mask = W.attention_mask(4096, 128, 0.01, seed=0)
+    Q, Km, V = (t.cuda() for t in W.attention_qkv(4, 8, 4096, 64, seed=1))
+    pos, crd, mv = mask.pos.cuda(), mask.crd.cuda(), mask.val.cuda()
+    plan = P.attention_plan(pos, crd, 64, 64)
+    assert isinstance(plan, K.AttnBandPlan) and plan.inside + plan.rem_nnz == mask.nnz
+    O = K.sparse_attention_csr(pos, crd, mv, Q, Km, V, scale=0.125, attn_plan=plan)
+    assert K.attn_band_status() == 0
+    O_blocks = K.sparse_attention_csr(pos, crd, mv, Q, Km, V, scale=0.125, attn_plan=K.attn_plan_for(pos, crd))
+    torch.testing.assert_close(O, O_blocks, rtol=RTOL, atol=ATOL)
+    assert torch.equal(O, K.sparse_attention_csr(pos, crd, mv, Q, Km, V, scale=0.125, attn_plan=plan))
+    O2 = K.sparse_attention_csr(pos, crd, mv, Q, Km, 2 * V + 1, scale=0.125, attn_plan=plan)
+    torch.testing.assert_close(O2, 2 * O + 1, rtol=RTOL, atol=2 * ATOL)      # softmax rows sum to one
+    pn, cn, mn = mask.pos.numpy(), mask.crd.numpy(), mask.val.numpy()
+    for u in (0, 13, 31):
+        s64 = oracle.sddmm_csr_acc64(pn, cn, mn, Q[u].cpu().numpy(), Km[u].cpu().numpy()) * 0.125
+        p64 = oracle.csr_row_softmax_acc64(pn, s64)
+        check(oracle, O[u].cpu().numpy(), oracle.spmm_csr_acc64(pn, cn, p64.astype(np.float32), V[u].cpu().numpy()),
+              f"one-call attention output head {u}")
+
+
 def test_c3_full_sae_decode(oracle):
     from scorch_b200 import kernels as K, workloads as W
     A = W.sae_activations(8192, 32768, 32, seed=0, device="cuda")
