@@ -731,6 +731,7 @@ static int band_check(int64_t m, int64_t n, int64_t d, int64_t nnz, const float*
                "sparse_attention_band: bad size");
   SB_CHECK_ARG(batch >= 1 && batch <= 65535, "sparse_attention_band: batch must be in [1, 65535]");
   SB_CHECK_ARG(d == 64, "sparse_attention_band: head dimension must be 64");
+  if (m == 0) return SB_OK;   // (nothing to do: the callers return before any pointer is used)
   SB_CHECK_ARG(Q && K && V && O, "sparse_attention_band: null pointer");
   SB_CHECK_ARG(ldq >= d && ldk >= d && ldv >= d && ldo >= d, "sparse_attention_band: row pitch smaller than d");
   auto aligned32 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; };

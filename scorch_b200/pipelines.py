@@ -158,3 +158,87 @@ class HostSparseAttention:
         main.wait_stream(self.s_out)
         main.synchronize()
         return out_host
+
+
+class HostGcnForward:
+    """The two-layer GCN forward  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329)
+    for features that live in pinned host memory and a result that goes back there, with the
+    copies overlapped with the kernels instead of put around them:
+
+    * the rows of X arrive in ``in_chunks`` pieces on a copy stream; the first layer runs as
+      accumulating SpMM passes over the same row chunks (``sharded._pipelined_layer``), so the
+      transform and the pass of chunk c start when chunk c has arrived — the layer costs about
+      the PCIe time of X plus its last pass instead of copy + layer;
+    * with one rank the second layer is cut into ``out_blocks`` row blocks (balanced by stored
+      entries); the rows of block b go back to the host while block b+1 is multiplied.  With
+      several ranks the second layer runs as in ``sharded.gcn_forward_sharded`` and the rank's
+      rows are copied back at the end.
+
+    ``pos, crd, val``: the global normalised adjacency matrix in CSR on the device; every rank
+    keeps its row block (and its own split by row chunk)."""
+
+    def __init__(self, pos, crd, val, W1: torch.Tensor, W2: torch.Tensor, rank: int = 0, world: int = 1,
+                 group=None, in_chunks: int = 8, out_blocks: int = 8):
+        from . import sharded as S
+        self.S, self.group = S, group
+        self.W1, self.W2 = W1, W2
+        dev = pos.device
+        # one rank: equal pieces (the copy is the pace-maker); several ranks: the split tuned for the gathers
+        self.shard = (S.ShardedCsr.from_global(pos, crd, val, rank, world, chunks=in_chunks, chunks2=1)
+                      if world == 1 else S.ShardedCsr.from_global(pos, crd, val, rank, world))
+        self.rows = self.shard.rows
+        self.k_in, self.k_out = W1.shape[0], W2.shape[1]
+        self.x = torch.empty((self.rows, self.k_in), dtype=torch.float32, device=dev)
+        self.out = torch.empty((self.rows, self.k_out), dtype=torch.float32, device=dev)
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.out_blocks = []
+        if world == 1:
+            local = self.shard.local
+            bounds = S.row_bounds(local.pos, max(1, min(out_blocks, max(1, self.rows))))
+            for b in range(len(bounds) - 1):
+                blk, _ = S.row_block(local.pos, local.crd, local.val, b, len(bounds) - 1, bounds=bounds)
+                self.out_blocks.append((bounds[b], bounds[b + 1], blk))
+            self.t2 = torch.empty((self.rows, self.k_out), dtype=torch.float32, device=dev)
+
+    def __call__(self, x_host: torch.Tensor, out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        S, shard = self.S, self.shard
+        if tuple(x_host.shape) != (self.rows, self.k_in):
+            raise ValueError(f"x_host must hold this rank's rows: {(self.rows, self.k_in)}")
+        if out_host is None:
+            out_host = torch.empty((self.rows, self.k_out), dtype=torch.float32, pin_memory=True)
+        main = torch.cuda.current_stream()
+        self.s_in.wait_stream(main)       # earlier readers of the staging buffers are done
+        self.s_out.wait_stream(main)
+        offsets = shard.splits[0].offsets
+        ready = []
+        with torch.cuda.stream(self.s_in):
+            for c in range(len(offsets) - 1):
+                lo, hi = min(offsets[c], self.rows), min(offsets[c + 1], self.rows)
+                if hi > lo:
+                    self.x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.s_in)
+                ready.append(ev)
+        if shard.world > 1:
+            out = S.gcn_forward_sharded(shard, self.x, self.W1, self.W2, group=self.group, x_ready=ready)
+            out_host.copy_(out, non_blocking=True)
+            main.synchronize()
+            return out_host
+        # (no look-ahead: with one rank there is no gather to keep busy, and chunk c's pass should not wait
+        # for chunk c + 2 to arrive)
+        H = S.gcn_forward_sharded(shard, self.x, self.W1, self.W2, x_ready=ready, first_layer_only=True,
+                                  lookahead=0)
+        torch.matmul(H, self.W2, out=self.t2)
+        for r0, r1, blk in self.out_blocks:
+            if r1 == r0:
+                continue
+            S.sharded_spmm_replicated(blk, self.t2, out=self.out[r0:r1])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                out_host[r0:r1].copy_(self.out[r0:r1], non_blocking=True)
+        main.wait_stream(self.s_out)
+        main.synchronize()
+        return out_host

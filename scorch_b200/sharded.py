@@ -44,7 +44,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass, field
-from typing import Callable, List, Optional
+from typing import Callable, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -350,8 +350,11 @@ class _Gatherer:
 
 def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x_local: torch.Tensor,
                      weight: Optional[torch.Tensor], out: torch.Tensor, relu: bool,
-                     spmm_fn: Callable, lookahead: int, tl: Optional[Timeline], label: str) -> None:
-    """out = act(A (x_local W)) over this rank's rows, chunk by chunk (W = None: act(A x))."""
+                     spmm_fn: Callable, lookahead: int, tl: Optional[Timeline], label: str,
+                     x_ready: Optional[Sequence] = None) -> None:
+    """out = act(A (x_local W)) over this rank's rows, chunk by chunk (W = None: act(A x)).
+    ``x_ready``: one CUDA event per chunk after which that chunk's rows of ``x_local`` are valid
+    (rows that are still arriving, e.g. by a host-to-device copy on another stream)."""
     S, dev = split.chunks, x_local.device
     k = out.shape[1]
     send = shard.buffer(name + "send", (shard.max_rows, k), dev)
@@ -372,6 +375,8 @@ def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x
         lo, hi = min(split.offsets[c], shard.rows), min(split.offsets[c + 1], shard.rows)
         produced = None
         with torch.cuda.stream(side) if side is not None else _span(None, ""):
+            if x_ready is not None and x_ready[c] is not None:
+                (side if side is not None else g.main).wait_event(x_ready[c])
             if hi > lo:
                 with _span(tlg, "dense_transform", side):
                     if weight is not None:
@@ -418,7 +423,8 @@ def sharded_layer(shard: ShardedCsr, x_local: torch.Tensor, weight: Optional[tor
 
 def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor,
                         group=None, spmm_fn: Optional[Callable] = None, lookahead: int = 2,
-                        timeline: Optional[Timeline] = None) -> torch.Tensor:
+                        timeline: Optional[Timeline] = None, x_ready: Optional[Sequence] = None,
+                        first_layer_only: bool = False) -> torch.Tensor:
     """This rank's rows of  A_hat ReLU(A_hat X W1) W2  (reference caller: bench/bench_gcn.py:314-329;
     transform first, then the sparse product, as there).
 
@@ -426,7 +432,9 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
     sub-matrices of earlier chunks are multiplied; transforms run ``lookahead`` chunks ahead of
     the SpMMs on the main stream so that the communication stream always has a gather queued.
     Exposed communication is one chunk's transform + gather at the start of each layer.  With one
-    rank and one chunk every layer is a single full-width SpMM."""
+    rank and one chunk every layer is a single full-width SpMM.
+    ``x_ready``: per first-layer chunk, the event after which that chunk's rows of ``x_local`` are
+    valid; ``first_layer_only``: return the hidden layer ReLU(A_hat X W1) (this rank's rows)."""
     spmm_fn = spmm_fn or _default_spmm
     lookahead = int(os.environ.get("SCORCH_B200_GCN_LOOKAHEAD", lookahead))
     dev = x_local.device
@@ -435,7 +443,9 @@ def gcn_forward_sharded(shard: ShardedCsr, x_local: torch.Tensor, W1: torch.Tens
     H = shard.buffer("hidden", (shard.rows, k1), dev)
     out = torch.empty((shard.rows, k2), dtype=torch.float32, device=dev)
     _pipelined_layer(shard, shard.splits[0], g, "l1", x_local, W1, H, True, spmm_fn, lookahead, timeline,
-                     "spmm_layer1")
+                     "spmm_layer1", x_ready=x_ready)
+    if first_layer_only:
+        return H
     _pipelined_layer(shard, shard.splits[-1], g, "l2", H, W2, out, False, spmm_fn, lookahead, timeline,
                      "spmm_layer2")
     if timeline is not None:

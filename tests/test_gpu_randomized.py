@@ -125,3 +125,31 @@ def test_spgemm_and_elementwise_random(oracle, A, seed_b):
         wp, wc, wv = oracle.csr_ewise(op, pos, crd, val, p2, c2, v2)
         assert np.array_equal(gp.cpu().numpy(), wp) and np.array_equal(gc.cpu().numpy(), wc)
         assert np.array_equal(gv.cpu().numpy(), wv)
+
+
+@settings(**dict(SETTINGS, max_examples=25))
+@given(csr_matrices(max_rows=300, max_cols=500), st.sampled_from([32, 64]), st.booleans(), st.booleans())
+def test_one_call_attention_random(oracle, A, d, band, pattern_only):
+    """Both tensor-core paths of the one-call attention on arbitrary masks (any mask is valid for
+    either plan: what does not fit the blocks / windows goes through the scattered-entry kernel)."""
+    from scorch_b200 import kernels as K
+    m, n, pos, crd, val, rng = A
+    if band and d != 64:
+        d = 64
+    mval = np.ones_like(val) if pattern_only else (np.abs(val) + 0.5).astype(np.float32)
+    Q = (rng.standard_normal((2, m, d)) * 0.5).astype(np.float32)
+    Km = (rng.standard_normal((2, n, d)) * 0.5).astype(np.float32)
+    V = rng.standard_normal((2, n, d)).astype(np.float32)
+    p, c = dev(pos), dev(crd)
+    plan = K.AttnBandPlan(p, c, n=n) if band else K.AttnPlan(p, c, n=n)
+    got = K.sparse_attention_csr(p, c, dev(mval), dev(Q), dev(Km), dev(V), scale=0.2, attn_plan=plan)
+    if band:
+        assert K.attn_band_status() == 0
+    for u in range(2):
+        s64 = oracle.sddmm_csr_acc64(pos, crd, mval, Q[u], Km[u]) * 0.2
+        p64 = oracle.csr_row_softmax_acc64(pos, s64)
+        want = oracle.spmm_csr_acc64(pos, crd, p64.astype(np.float32), V[u])
+        ok, err, bad = oracle.allclose_report(got[u].cpu().numpy(), want, RTOL, ATOL)
+        assert ok, (m, n, d, band, err, bad)
+    assert torch.equal(got, K.sparse_attention_csr(p, c, dev(mval), dev(Q), dev(Km), dev(V), scale=0.2,
+                                                   attn_plan=plan))

@@ -96,6 +96,30 @@ def test_chunked_gcn_one_gpu_matches_unchunked(oracle, chunks):
         assert ok, (r, err, bad)
 
 
+@pytest.mark.parametrize("in_chunks,out_blocks", [(8, 8), (3, 5), (1, 1)])
+def test_host_tensor_gcn_forward_overlaps_copies_and_matches(oracle, in_chunks, out_blocks):
+    """Features in pinned host memory, result back there: chunked host-to-device copy feeding the
+    accumulating first-layer passes, second layer in row blocks copied back as they finish."""
+    from scorch_b200 import pipelines as P, workloads as W
+    n = 20000
+    g = W.gcn_graph(n, mean_deg=30.0, max_deg=5000, seed=0).to("cuda")
+    X = W.randn_on((n, 256), seed=1)
+    W1, W2 = W.glorot(256, 256, seed=0).cuda(), W.glorot(256, 64, seed=1).cuda()
+    host = P.HostGcnForward(g.pos, g.crd, g.val, W1, W2, in_chunks=in_chunks, out_blocks=out_blocks)
+    xh = X.pin_memory()
+    out1 = host(xh).clone()
+    out_h = torch.empty((n, 64), dtype=torch.float32).pin_memory()
+    out2 = host(xh, out_h)                       # buffers and streams are reused across calls
+    assert out2 is out_h and torch.equal(out1, out2)
+    single = P.gcn_forward(g.pos, g.crd, g.val, X.cuda(), W1, W2).cpu()
+    torch.testing.assert_close(out2, single, rtol=1e-4, atol=1e-5)
+    pos, crd, val = (t.cpu().numpy() for t in (g.pos, g.crd, g.val))
+    h = np.maximum(oracle.spmm_csr_acc64(pos, crd, val, (X.double() @ W1.cpu().double()).float().numpy()), 0)
+    want = oracle.spmm_csr_acc64(pos, crd, val, (h @ W2.cpu().double().numpy()).astype(np.float32))
+    ok, err, bad = oracle.allclose_report(out2.numpy(), want, 2e-3, 1e-4)
+    assert ok, (err, bad)
+
+
 def test_replicated_operand_row_blocks(oracle):
     """Row blocks of a rectangular matrix against a dense operand every rank holds: the blocks'
     results stacked in rank order are the whole product (no communication involved)."""
