@@ -38,6 +38,11 @@ def _worker(rank, world, port, n, tmp):
         for _ in range(2):  # twice: buffers and streams are reused across steps
             out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2)
         full = S.gather_rows(shard, out)
+        # the host-tensor front end: this rank's rows from pinned memory and back
+        from scorch_b200 import pipelines as P
+        host = P.HostGcnForward(g.pos, g.crd, g.val, W1, W2, rank, world)
+        back = host(X[r0:r1].cpu().pin_memory())
+        assert torch.allclose(back, out.cpu(), rtol=1e-4, atol=1e-5)
         torch.cuda.synchronize()
         if rank == 0:
             torch.save(full.cpu(), tmp)
