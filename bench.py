@@ -30,6 +30,7 @@ reported step time is that of the median block.
 from __future__ import annotations
 
 import argparse
+import datetime
 import hashlib
 import json
 import os
@@ -1028,7 +1029,9 @@ def main():
     _bind_to_gpu_numa_node(local_rank)
     import torch.distributed as dist
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # (a rank that dies leaves the others in a collective: give up after four minutes, not ten)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=240))
 
     def barrier():
         if world > 1:
