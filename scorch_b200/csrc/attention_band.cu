@@ -662,11 +662,9 @@ static size_t band_smem_bytes() {
 template <int D>
 static int band_launch(const AttnArgs& a, const BandArgs& b, unsigned tiles, unsigned batch, cudaStream_t st) {
   const size_t smem = band_smem_bytes<D>();
-  static bool configured = false;   // (per template instance; the attribute is per device function)
-  if (!configured) {
-    SB_CUDA(cudaFuncSetAttribute(attn_band_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  // (set on every call: the attribute belongs to the current device's copy of the function, and a
+  // process may drive more than one device)
+  SB_CUDA(cudaFuncSetAttribute(attn_band_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   attn_band_kernel<D><<<dim3(tiles, batch), kBandThreads, smem, st>>>(a, b);
   SB_LAUNCH_CHECK("attn_band_kernel");
   return SB_OK;
