@@ -174,12 +174,18 @@ class HostGcnForward:
       several ranks the second layer runs as in ``sharded.gcn_forward_sharded`` and the rank's
       rows are copied back at the end.
 
+    Measured on B200 (2 M nodes, 2.05 GB in, 0.51 GB out): 82 ms with copy -> forward -> copy, 51.9 ms
+    with 8 chunks / 8 blocks, 50.7 ms with 16 / 16, 61.5 ms with 32 / 16 (the X copy alone is 37 ms).
+
     ``pos, crd, val``: the global normalised adjacency matrix in CSR on the device; every rank
     keeps its row block (and its own split by row chunk)."""
 
     def __init__(self, pos, crd, val, W1: torch.Tensor, W2: torch.Tensor, rank: int = 0, world: int = 1,
-                 group=None, in_chunks: int = 8, out_blocks: int = 8):
+                 group=None, in_chunks: int = 16, out_blocks: int = 16):
         from . import sharded as S
+        env = os.environ.get("SCORCH_B200_HOST_GCN_CHUNKS")      # "<in_chunks>,<out_blocks>"
+        if env:
+            in_chunks, out_blocks = (int(x) for x in env.split(","))
         self.S, self.group = S, group
         self.W1, self.W2 = W1, W2
         dev = pos.device

@@ -101,7 +101,7 @@ def test_chunked_gcn_one_gpu_matches_unchunked(oracle, chunks):
         assert ok, (r, err, bad)
 
 
-@pytest.mark.parametrize("in_chunks,out_blocks", [(8, 8), (3, 5), (1, 1)])
+@pytest.mark.parametrize("in_chunks,out_blocks", [(16, 16), (8, 8), (3, 5), (1, 1)])
 def test_host_tensor_gcn_forward_overlaps_copies_and_matches(oracle, in_chunks, out_blocks):
     """Features in pinned host memory, result back there: chunked host-to-device copy feeding the
     accumulating first-layer passes, second layer in row blocks copied back as they finish."""
