@@ -49,6 +49,12 @@ def _worker(rank, world, port, n, chunks, tmp):
         out = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, spmm_fn=_oracle_spmm)
         one = S.sharded_layer(shard, X[r0:r1].contiguous(), W1, relu=True, spmm_fn=_oracle_spmm)
         assert one.shape == (r1 - r0, 40)
+        # the same forward without look-ahead, and its first layer alone (what the host-tensor front end calls)
+        out0 = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, spmm_fn=_oracle_spmm, lookahead=0)
+        assert torch.equal(out0, out)
+        hid = S.gcn_forward_sharded(shard, X[r0:r1].contiguous(), W1, W2, spmm_fn=_oracle_spmm,
+                                    first_layer_only=True)
+        assert torch.equal(hid, one)
         full, full_one = S.gather_rows(shard, out), S.gather_rows(shard, one)
         if rank == 0:
             torch.save({"out": full, "one": full_one, "bounds": shard.bounds, "max_rows": shard.max_rows,
