@@ -279,3 +279,35 @@ def csr_ewise(op, Apos, Acrd, Aval, Bpos, Bcrd, Bval):
         pos.append(len(crd))
     return (np.asarray(pos, np.int32), np.asarray(crd, np.int32),
             np.asarray(val, Aval.dtype) if val else np.zeros(0, Aval.dtype))
+
+
+# ---- 3-D compressed-fibre tensors (numpy) ---------------------------------------------------
+def csf3_to_dense(shape, levels, val):
+    """Dense (I, J, K) array of a tensor in the reference's ``d,s,s`` / ``s,s,s`` layout
+    (src/scorch/storage.py, format.py:7-27): ``levels[0]`` is ``[]`` (dense i) or ``[pos0, crd0]``
+    (the stored i slices), ``levels[1] = [pos1, crd1]`` the j of every stored (i, j) fibre,
+    ``levels[2] = [pos2, crd2]`` the k of every entry of a fibre; ``val`` in that order."""
+    I, J, K = shape
+    out = np.zeros((I, J, K), dtype=np.float64)
+    pos1, crd1 = (np.asarray(x) for x in levels[1])
+    pos2, crd2 = (np.asarray(x) for x in levels[2])
+    slices = np.asarray(levels[0][1]) if len(levels[0]) else np.arange(I)
+    val = np.asarray(val)
+    for r in range(len(pos1) - 1):
+        for f in range(pos1[r], pos1[r + 1]):
+            for p in range(pos2[f], pos2[f + 1]):
+                out[slices[r], crd1[f], crd2[p]] = val[p]
+    return out
+
+
+def ttm_acc64(shape, levels, val, B):
+    """C[i,j,m] = sum_k A[i,j,k] B[k,m] in float64 (the reference compiles this from
+    einsum("ijk,km->ijm"), tests/test_scorch/test_kernels_comprehensive.py:418-445)."""
+    return np.einsum("ijk,km->ijm", csf3_to_dense(shape, levels, val), np.asarray(B, np.float64))
+
+
+def mttkrp_acc64(shape, levels, val, B, C):
+    """D[i,m] = sum_jk A[i,j,k] B[j,m] C[k,m] in float64 (einsum("ijk,jm,km->im"),
+    tests/test_scorch/test_kernels_comprehensive.py:450-482)."""
+    return np.einsum("ijk,jm,km->im", csf3_to_dense(shape, levels, val), np.asarray(B, np.float64),
+                     np.asarray(C, np.float64))

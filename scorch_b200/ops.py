@@ -171,7 +171,9 @@ def einsum(expression: str, *tensors: Union[torch.Tensor, STensor], **kwargs: An
       A COO mask gives a result sharing the mask's coordinates (prebuilt route, ops.py:396-423);
       a CSR mask gives an all-COO result with fresh int32 coordinates in mask order, which is
       what the reference's compiler emits (ops.py:638-664).
-    * ``"ij,jk->ik"`` -> ``matmul``;  ``"ij,j->i"`` -> SpMV.
+    * ``"ij,jk->ik"`` -> ``matmul``;  ``"ij,j->i"`` -> SpMV;  ``"ij,ij->ij"`` -> element-wise product.
+    * ``"ijk,km->ijm"`` (TTM) and ``"ijk,jm,km->im"`` (MTTKRP) with a ``d,s,s`` / ``s,s,s`` (or dense)
+      3-D tensor and dense matrices -> dense result (``tensor3``).
     """
     ts = tuple(STensor.from_torch(t) if isinstance(t, torch.Tensor) else t for t in tensors)
     expr = expression.replace(" ", "")
@@ -199,6 +201,15 @@ def einsum(expression: str, *tensors: Union[torch.Tensor, STensor], **kwargs: An
         return matmul(ts[0], ts[1], **kwargs)
     if expr == "ij,j->i" and len(ts) == 2:
         return matmul(ts[0], ts[1], **kwargs)
+    if expr in ("ijk,km->ijm", "ijk,jm,km->im"):
+        # TTM / MTTKRP of a compressed-fibre tensor: CSR x dense products over its fibre matrix
+        from . import tensor3
+        requested = kwargs.get("format", kwargs.get("output_format"))
+        if requested is not None and not parse_format(requested).is_dense():
+            raise NotImplementedError("3-D contractions produce dense results")
+        r = tensor3.contract(expr, ts[0], *ts[1:])
+        if r is not None:
+            return STensor.from_torch(r[0])
     raise NotImplementedError(
         f"einsum expression {expression!r} is outside the sparse hot path (SpMM, SDDMM, SpMV, "
         "SpGEMM); the reference would JIT-compile it")

@@ -166,5 +166,26 @@ for name, dtype in (("ewise_f32", np.float32),):
         add_pos=total.index.mode_indices[1][0], add_crd=total.index.mode_indices[1][1], add_val=total.values,
         add_format=np.array([str(total.format)]), n=np.array([27]))
 
+# ---- 3-D compressed-fibre tensor times matrices: TTM and MTTKRP (compiler-emitted loops) ----------------
+def csf_arrays(st):
+    lv = st.index.mode_indices
+    arrays = {"pos1": lv[1][0], "crd1": lv[1][1], "pos2": lv[2][0], "crd2": lv[2][1], "val": st.values}
+    if len(lv[0]):
+        arrays.update(pos0=lv[0][0], crd0=lv[0][1])
+    return arrays
+
+
+T3 = torch.from_numpy((rng.standard_normal((7, 6, 9)).astype(np.float32)) * (rng.random((7, 6, 9)) < 0.3))
+T3[2] = 0            # an i slice without entries
+T3[:, 4, :] = 0      # a j that no fibre uses
+Bm = torch.from_numpy(rng.standard_normal((9, 5)).astype(np.float32))     # (K, M)
+Bj = torch.from_numpy(rng.standard_normal((6, 5)).astype(np.float32))     # (J, M)
+for fmt in ("dss", "sss"):
+    a_st = STensor.from_torch(T3).to_sparse(fmt)
+    ttm = scorch.einsum("ijk,km->ijm", a_st, STensor.from_torch(Bm), format="ddd")
+    mk = scorch.einsum("ijk,jm,km->im", a_st, STensor.from_torch(Bj), STensor.from_torch(Bm), format="dd")
+    put("tensor3_" + fmt, shape=np.array(T3.shape), dense=T3, B_km=Bm, B_jm=Bj,
+        ttm=ttm.to_torch(), mttkrp=mk.to_torch(), format=np.array([str(a_st.format)]), **csf_arrays(a_st))
+
 np.savez_compressed(os.path.join(HERE, "hotpath_golden.npz"), **out)
 print("wrote", len(out), "arrays;", sum(v.nbytes for v in out.values()), "bytes")
