@@ -286,6 +286,29 @@ SB_API int sb_sparse_attention_csr_f32(int64_t m, int64_t n, int64_t d, int64_t 
                                        int stages, void* stream);
 
 /* --------------------------------------------------------------------------------------------
+ * CSR input validation (no counterpart in the reference, whose loops trust their inputs like the
+ * kernels here: csrc/spmm.h:2035-2077 never checks crd against the operand's height).  Finds the
+ * first entry that would make a kernel of this library read or write outside its arrays, reading
+ * nothing outside pos[0..m] and crd[0..nnz): row pointers first, then — only if those are valid —
+ * the columns of every row.  report_host[0] = one of the codes below (0: valid), [1] = row,
+ * [2] = entry index (column checks), [3] = the offending value; the smallest (row, entry) is
+ * reported whatever the scheduling.  sorted_unique != 0 also requires strictly ascending columns
+ * per row (SpGEMM, the element-wise kernels, the attention plans and the transposes rely on it).
+ * Synchronises the stream.  `ws`: sb_csr_validate_workspace_bytes() bytes, 16-byte aligned.
+ * The Python layer runs it on every CSR operand when SCORCH_B200_VALIDATE=1.
+ * -------------------------------------------------------------------------------------------- */
+#define SB_CSR_BAD_FIRST_POS 1
+#define SB_CSR_BAD_LAST_POS 2
+#define SB_CSR_POS_OUT_OF_RANGE 3
+#define SB_CSR_POS_DECREASES 4
+#define SB_CSR_COLUMN_OUT_OF_RANGE 5
+#define SB_CSR_COLUMNS_NOT_ASCENDING 6
+SB_API size_t sb_csr_validate_workspace_bytes(void);
+SB_API int sb_csr_validate(int64_t m, int64_t n, int64_t nnz, const int32_t* pos, const int32_t* crd,
+                           int sorted_unique, int32_t* report_host, void* ws, size_t ws_bytes,
+                           void* stream);
+
+/* --------------------------------------------------------------------------------------------
  * The same sparse attention for banded masks on the tcgen05 tensor cores (head dimension 64).
  * Replaces: the same operator sequence (bench/bench_sparse_transformer.py:304-382).
  * A band plan cuts the mask rows into tiles of SB_ATTN_BAND_ROWS rows and gives tile t the window

@@ -62,6 +62,8 @@ SIGNATURES = {
     "sb_sparse_attention_csr_f32": (_int, [_i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr,
                                            _i64, _ptr, _i64, _f32, _ptr, _i64, _i64, _i64, _i64, _i64,
                                            _i64, _ptr, _i64, _i64, _ptr, _sz, _int, _ptr]),
+    "sb_csr_validate_workspace_bytes": (_sz, []),
+    "sb_csr_validate": (_int, [_i64, _i64, _i64, _ptr, _ptr, _int, _ptr, _ptr, _sz, _ptr]),
     "sb_attn_band_plan_bytes": (_sz, [_i64, _i64]),
     "sb_attn_band_plan_build": (_int, [_i64, _i64, _i64, _ptr, _ptr, _ptr, _sz, C.POINTER(_i64),
                                        C.POINTER(_i64), _ptr]),

@@ -7,6 +7,7 @@ path lives in ``scorch_ops``).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple, Union
 
 import torch
@@ -39,6 +40,36 @@ def _wrote(t: torch.Tensor) -> torch.Tensor:
     plans, the all-ones verdict of a mask) is not reused for the new contents."""
     torch.autograd.graph.increment_version(t)
     return t
+
+
+CSR_VIOLATIONS = {1: "pos[0] is not 0", 2: "pos[m] is not nnz", 3: "row pointer out of [0, nnz]",
+                  4: "row pointers decrease", 5: "column index out of range", 6: "columns of a row not strictly ascending"}
+
+
+def csr_validate(pos: torch.Tensor, crd: torch.Tensor, n: int, sorted_unique: bool = True):
+    """Device-side check of a CSR structure against what the kernels assume (they trust their
+    inputs, like the reference's loops).  Returns None when it is valid, else
+    ``(message, row, entry, value)`` for the first violation (smallest row, then entry)."""
+    pos, crd = _dev(pos, torch.int32, "pos"), _dev(crd, torch.int32, "crd")
+    L = _lib.lib()
+    ws = torch.empty(L.sb_csr_validate_workspace_bytes(), dtype=torch.uint8, device=pos.device)
+    report = (C.c_int32 * 4)()
+    with torch.cuda.device(pos.device):
+        check(L.sb_csr_validate(pos.numel() - 1, int(n), crd.numel(), pos.data_ptr(), _ptr(crd),
+                                1 if sorted_unique else 0, report, ws.data_ptr(), ws.numel(), _stream()))
+    if report[0] == 0:
+        return None
+    return CSR_VIOLATIONS.get(report[0], f"code {report[0]}"), int(report[1]), int(report[2]), int(report[3])
+
+
+def _validated(pos, crd, n: int, what: str, sorted_unique: bool = False) -> None:
+    """With SCORCH_B200_VALIDATE=1 every CSR operand is checked before a kernel reads it (a
+    synchronising pass over pos and crd: a debugging aid, off by default)."""
+    if os.environ.get("SCORCH_B200_VALIDATE") != "1":
+        return
+    bad = csr_validate(pos, crd, n, sorted_unique)
+    if bad is not None:
+        raise ValueError(f"{what}: invalid CSR operand: {bad[0]} (row {bad[1]}, entry {bad[2]}, value {bad[3]})")
 
 
 class CsrPlan:
@@ -331,6 +362,7 @@ def spmm_csr(pos, crd, val, B, bias=None, relu: bool = False, plan: Optional[Csr
     B = B.contiguous() if batched else _row_major_2d(B, "B")
     batch = B.shape[0] if batched else 1
     nb, k = B.shape[-2], B.shape[-1]
+    _validated(pos, crd, nb, "spmm_csr")
     ldb = k if batched else B.stride(0)
     if val.dim() == 2:
         if val.shape[0] != batch or val.shape[1] != nnz:
@@ -412,6 +444,7 @@ def spmv_csr(pos, crd, val, x, plan: Optional[CsrPlan] = None) -> torch.Tensor:
         raise TypeError(f"unsupported value dtype {val.dtype}")
     val = _dev(val, val.dtype, "val")
     x = _dev(x, val.dtype, "x")
+    _validated(pos, crd, x.numel(), "spmv_csr")
     y = torch.empty(m, dtype=val.dtype, device=x.device)
     L = _lib.lib()
     with torch.cuda.device(x.device):
@@ -445,6 +478,7 @@ def sddmm_csr(pos, crd, mask_val, Q, K, want_coords: bool = False,
     crd = _dev(crd, torch.int32, "crd")
     Q, K, batch = _qk(Q, K)
     m, nnz, d = pos.numel() - 1, crd.numel(), Q.shape[-1]
+    _validated(pos, crd, K.shape[-2], "sddmm_csr")
     if mask_val is not None:
         mask_val = _dev(mask_val, torch.float32, "mask_val")
     shape = (batch, nnz) if Q.dim() == 3 else (nnz,)
@@ -513,6 +547,8 @@ def spgemm_csr(Apos, Acrd, Aval, Bpos, Bcrd, Bval, n: int, timings: Optional[dic
         raise TypeError("SpGEMM operands must share one of f32/f64/i32/i64")
     Aval, Bval = _dev(Aval, Aval.dtype, "Aval"), _dev(Bval, Aval.dtype, "Bval")
     m, kb = Apos.numel() - 1, Bpos.numel() - 1
+    _validated(Apos, Acrd, kb, "spgemm_csr (A)", sorted_unique=True)
+    _validated(Bpos, Bcrd, n, "spgemm_csr (B)", sorted_unique=True)
     L = _lib.lib()
     dev = Aval.device
     with torch.cuda.device(dev):
