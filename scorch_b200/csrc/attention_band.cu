@@ -8,15 +8,19 @@
 // values); the entries outside go to a CSR remainder list, which the scattered-entry kernel of
 // attention.cu handles first, leaving per row an unnormalised output and (maximum, sum).
 //
-// attn_band_kernel, one CTA (256 threads) per (tile, head):
-//   1. Q tile and K window rows are read with plain loads, split into TF32 hi / lo parts and
-//      stored to shared memory in the tensor core's canonical K-major layout without swizzle
-//      (core matrix = 8 rows x 16 bytes, the cores of one 8-row group side by side);
-//   2. one thread issues  S = Q K^T  as tcgen05.mma kind::tf32 (M 128, N 128, K 8) in three
-//      passes (lo*hi, hi*lo, hi*hi: the 3xTF32 split, fp32-level accuracy) into 384 TMEM columns;
-//   3. every thread owns one row and half of the columns: it reads its scores with tcgen05.ld,
-//      masks the entries that are not stored, applies scale and mask values, and after the row
-//      maxima are known writes P = exp2(S - max) back as hi (in place) and lo (64 spare columns);
+// attn_band_kernel, one CTA of nine warps per (tile, head): eight warps stage operands and own the
+// rows, lane 0 of the ninth issues the tensor-core work (so that issuing overlaps the others' work):
+//   1. Q tile and K window rows are read with plain loads (into registers ahead of the point where
+//      their shared-memory buffer is free), split into TF32 hi / lo parts and stored to shared
+//      memory in the tensor core's canonical K-major layout without swizzle (core matrix = 8 rows
+//      x 16 bytes, the cores of one 8-row group side by side);
+//   2. S = Q K^T  is issued as tcgen05.mma kind::tf32 (M 128, N 128, K 8) in three passes
+//      (lo*hi, hi*lo, hi*hi: the 3xTF32 split, fp32-level accuracy) into 384 TMEM columns, one K
+//      piece of 128 window columns at a time through two buffers;
+//   3. every thread of the eight warps owns one row and half of the columns: it reads its scores
+//      with tcgen05.ld, masks the entries that are not stored (without branches), applies scale
+//      and mask values, takes the row maxima piece by piece while the next piece's products run,
+//      and then writes P = exp2(S - max) back as hi (in place) and lo (64 spare columns);
 //   4. O += P V  is issued with P read from TMEM as the A operand and V^T (transposed while it is
 //      staged, so that it is K-major like K) as the B operand, 64 window columns at a time;
 //   5. the epilogue reads O from TMEM, merges the scattered entries' (max, sum, O) and writes O / sum.
