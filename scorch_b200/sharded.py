@@ -360,10 +360,12 @@ def _pipelined_layer(shard: ShardedCsr, split: Split, g: _Gatherer, name: str, x
     send = shard.buffer(name + "send", (shard.max_rows, k), dev)
     pending = []
     tlg = tl if dev.type == "cuda" else None
-    # the dense transforms run on a stream of their own, beside the SpMM passes (0.6 ms of 11.9 at
-    # four ranks); SCORCH_B200_GCN_TRANSFORM_STREAM=0 puts them back on the main stream
+    # with several ranks the dense transforms run on a stream of their own, beside the SpMM passes
+    # (0.6 ms of 11.9 at four ranks); SCORCH_B200_GCN_TRANSFORM_STREAM=0 puts them back on the main
+    # stream, =1 also moves them there for a chunked layer on one rank
     side = None
-    if dev.type == "cuda" and shard.world > 1 and os.environ.get("SCORCH_B200_GCN_TRANSFORM_STREAM", "1") != "0":
+    want_side = os.environ.get("SCORCH_B200_GCN_TRANSFORM_STREAM", "1" if shard.world > 1 else "0")
+    if dev.type == "cuda" and S > 1 and want_side != "0":
         side = shard._buffers.get("transform_stream")
         if side is None:
             side = shard._buffers["transform_stream"] = torch.cuda.Stream(device=dev)
