@@ -77,3 +77,32 @@ def test_argument_validation_returns_codes_without_launching(sb_lib):
         check(sb_lib.sb_spgemm_symbolic(4, 4, 4, one, one, one, one, one, C.pointer(C.c_int64(0)),
                                         one, 16, None))
     assert e.value.status == 4
+
+
+def test_argument_validation_of_the_attention_and_validation_entry_points(sb_lib):
+    one = C.c_void_p(32)  # never dereferenced: validation fails first
+    # band attention: head dimension 64 only, row pitch >= d, batch within the launch grid
+    common = lambda d, ld, batch: sb_lib.sb_sparse_attention_band_f32(
+        128, 128, d, 10, one, one, None, one, ld, one, ld, one, ld, 1.0, one, ld, batch, 0, 0, 0, 0,
+        one, 0, one, 1 << 20, 3, None)
+    assert common(32, 32, 1) == 1 and b"head dimension must be 64" in sb_lib.sb_last_error()
+    assert common(64, 32, 1) == 1 and b"row pitch" in sb_lib.sb_last_error()
+    assert common(64, 64, 70000) == 1 and b"batch" in sb_lib.sb_last_error()
+    rc = sb_lib.sb_sparse_attention_band_f32(128, 128, 64, 10, one, one, None, one, 64, one, 64, one, 64, 1.0,
+                                             one, 64, 1, 0, 0, 0, 0, one, 0, one, 1 << 20, 0, None)
+    assert rc == 1 and b"stage" in sb_lib.sb_last_error()
+    # an empty mask is nothing to do, whatever the pointers
+    assert sb_lib.sb_sparse_attention_band_f32(0, 128, 64, 0, None, None, None, None, 64, None, 64, None, 64, 1.0,
+                                               None, 64, 1, 0, 0, 0, 0, None, 0, None, 0, 3, None) == 0
+    rc = sb_lib.sb_attn_band_plan_build(4, 4, 4, one, one, one, 8, None, None, None)
+    assert rc == 4 and b"needs" in sb_lib.sb_last_error()
+    assert sb_lib.sb_attn_band_plan_bytes(4096, 1 << 20) > (2 << 20) * 4
+    rc = sb_lib.sb_attn_band_probe(128, 384, 64, 5, one, 64, one, 64, one, 64, one, None, None, None)
+    assert rc == 1 and b"tile out of range" in sb_lib.sb_last_error()
+    # CSR validation: sizes, pointers and the workspace are checked before anything is read
+    report = (C.c_int32 * 4)()
+    assert sb_lib.sb_csr_validate_workspace_bytes() == 32
+    assert sb_lib.sb_csr_validate(-1, 4, 4, one, one, 1, report, one, 32, None) == 1
+    assert sb_lib.sb_csr_validate(4, 4, 4, None, one, 1, report, one, 32, None) == 1
+    assert sb_lib.sb_csr_validate(4, 4, 4, one, one, 1, report, one, 8, None) == 1
+    assert b"workspace" in sb_lib.sb_last_error()
